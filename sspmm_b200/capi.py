@@ -1,0 +1,62 @@
+"""ctypes binding of libsspmm_b200.so (the C ABI in include/sspmm_b200.h).
+
+The library is the product: nothing here computes on the CPU, and importing
+this module raises if the shared object is missing (build it with
+``python -m sspmm_b200.build``)."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "lib", "libsspmm_b200.so")
+
+c_int_p = C.POINTER(C.c_int)
+_vp = C.c_void_p
+
+# name -> (restype, argtypes); mirrors include/sspmm_b200.h one to one
+SIGNATURES = {
+    "sspmm_f16_f32": (C.c_int, [C.c_int] * 4 + [_vp] * 7),
+    "sspmm_f16_f16": (C.c_int, [C.c_int] * 4 + [_vp] * 7),
+    "sspmm_f16_f16_batched": (C.c_int, [C.c_int] * 5 + [_vp, _vp, _vp, _vp, C.c_int64, _vp, C.c_int64, _vp, C.c_int64, _vp]),
+    "sspmm_set_kernel": (C.c_int, [C.c_int]),
+    "sspmm_device_status": (C.c_int, [c_int_p]),
+    "svc_begin": (C.c_int, [C.c_int] * 3 + [_vp, _vp, _vp, _vp, C.POINTER(_vp), C.POINTER(C.c_int64)]),
+    "svc_finish": (C.c_int, [_vp, _vp, _vp, _vp, _vp]),
+    "svc_free": (C.c_int, [_vp]),
+    "svc_replayed_rows": (C.c_int, [_vp, C.POINTER(C.c_int64)]),
+    "sspmm_sorted_row_swizzle": (C.c_int, [C.c_int, _vp, _vp, _vp]),
+    "sspmm_last_error_string": (C.c_char_p, []),
+    "sspmm_version": (C.c_char_p, []),
+}
+
+
+class SspmmError(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__(f"sspmm_b200 error {code}: {message}")
+        self.code = code
+
+
+def load(path: str = _LIB_PATH) -> C.CDLL:
+    if not os.path.exists(path):
+        raise ImportError(f"{path} not found: build it with `python -m sspmm_b200.build`")
+    lib = C.CDLL(path)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    return lib
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        _lib = load()
+    return _lib
+
+
+def check(rc: int) -> None:
+    if rc != 0:
+        raise SspmmError(rc, lib().sspmm_last_error_string().decode())

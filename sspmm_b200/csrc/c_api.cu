@@ -1,0 +1,279 @@
+// extern "C" entry points declared in include/sspmm_b200.h.
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <new>
+
+#include "../../include/sspmm_b200.h"
+#include "launch.h"
+#include "ptx.cuh"
+#include "svc.cuh"
+
+namespace sspmm_b200 {
+
+static thread_local char g_err[512] = "";
+
+void set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof g_err, fmt, ap);
+    va_end(ap);
+}
+
+static std::atomic<int> g_kernel_choice{0};
+
+static int fail(cudaError_t e, const char* what) {
+    if (g_err[0] == 0) set_error("%s: %s", what, cudaGetErrorString(e));
+    return (int)e;
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Length-sorted scheduling order: rank by (length descending, row id ascending).
+__global__ void __launch_bounds__(256)
+row_swizzle_kernel(int m_vec, const int* __restrict__ row_offsets, int* __restrict__ row_indices) {
+    __shared__ int tile_len[256];
+    const int i = blockIdx.x * 256 + threadIdx.x;
+    const int my = (i < m_vec) ? row_offsets[i + 1] - row_offsets[i] : 0;
+    int rank = 0;
+    for (int base = 0; base < m_vec; base += 256) {
+        const int k = base + threadIdx.x;
+        tile_len[threadIdx.x] = (k < m_vec) ? row_offsets[k + 1] - row_offsets[k] : -1;
+        __syncthreads();
+        const int lim = min(256, m_vec - base);
+        for (int t = 0; t < lim; ++t) {
+            const int l = tile_len[t];
+            rank += (l > my || (l == my && base + t < i)) ? 1 : 0;
+        }
+        __syncthreads();
+    }
+    if (i < m_vec) row_indices[rank] = i;
+}
+
+static int spmm_entry(int m_vec, int V, int N, int K, int batch, const int* row_indices, const int* row_offsets,
+                      const int* column_indices, const void* values, int64_t values_stride, const void* rhs,
+                      int64_t rhs_stride, void* out, int64_t out_stride, bool out_f16, void* stream) {
+    g_err[0] = 0;
+    if (V != 8 && V != 16) {
+        set_error("vec_length must be 8 or 16 (got %d)", V);
+        return (int)cudaErrorInvalidValue;
+    }
+    if (m_vec < 0 || N < 0 || K < 0 || batch < 0) {
+        set_error("negative dimension (m_vec=%d N=%d K=%d batch=%d)", m_vec, N, K, batch);
+        return (int)cudaErrorInvalidValue;
+    }
+    if (m_vec == 0 || N == 0 || batch == 0) return 0;
+    if (!row_offsets || !out || (K > 0 && (!column_indices || !values || !rhs))) {
+        set_error("null operand pointer");
+        return (int)cudaErrorInvalidValue;
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    SpmmArgs a;
+    a.m_vec = m_vec; a.V = V; a.N = N; a.K = K;
+    a.row_indices = row_indices; a.row_offsets = row_offsets; a.column_indices = column_indices;
+    a.values = static_cast<const __half*>(values); a.rhs = static_cast<const __half*>(rhs);
+    a.out = out; a.out_f16 = out_f16; a.batch = batch;
+    a.values_stride = values_stride; a.rhs_stride = rhs_stride; a.out_stride = out_stride;
+    a.stream = st;
+
+    const int choice = g_kernel_choice.load();
+    const bool tc_ok = K > 0 && (N % 8 == 0) && aligned16(rhs) && aligned16(values) &&
+                       (values_stride * 2) % 16 == 0 && (batch == 1 || rhs_stride == (int64_t)K * N);
+    if (choice == 1 && !tc_ok) {
+        set_error("tensor-core kernel needs N %% 8 == 0, 16-byte aligned values/rhs and contiguous batches");
+        return (int)cudaErrorInvalidValue;
+    }
+    cudaError_t e;
+    if (K == 0 || choice == 2 || !tc_ok) e = launch_sspmm_simt(a);
+    else e = launch_sspmm_gather(a);
+    return e == cudaSuccess ? 0 : fail(e, "SpMM launch");
+}
+
+}  // namespace sspmm_b200
+
+using namespace sspmm_b200;
+
+struct svc_job {
+    SvcProblem p;
+    SvcScratch s;
+    bool with_values;
+    long long nvec;
+    long long table_ints;
+    int device;
+    cudaStream_t stream;
+};
+
+extern "C" {
+
+int sspmm_f16_f32(int m_vec, int vec_length, int N, int K, const int* row_indices, const int* row_offsets,
+                  const int* column_indices, const void* values_f16, const void* rhs_f16, float* out_f32,
+                  void* stream) {
+    return spmm_entry(m_vec, vec_length, N, K, 1, row_indices, row_offsets, column_indices, values_f16, 0, rhs_f16, 0,
+                      out_f32, 0, false, stream);
+}
+
+int sspmm_f16_f16(int m_vec, int vec_length, int N, int K, const int* row_indices, const int* row_offsets,
+                  const int* column_indices, const void* values_f16, const void* rhs_f16, void* out_f16, void* stream) {
+    return spmm_entry(m_vec, vec_length, N, K, 1, row_indices, row_offsets, column_indices, values_f16, 0, rhs_f16, 0,
+                      out_f16, 0, true, stream);
+}
+
+int sspmm_f16_f16_batched(int m_vec, int vec_length, int N, int K, int batch, const int* row_indices,
+                          const int* row_offsets, const int* column_indices, const void* values_f16,
+                          int64_t values_stride, const void* rhs_f16, int64_t rhs_stride, void* out_f16,
+                          int64_t out_stride, void* stream) {
+    return spmm_entry(m_vec, vec_length, N, K, batch, row_indices, row_offsets, column_indices, values_f16,
+                      values_stride, rhs_f16, rhs_stride, out_f16, out_stride, true, stream);
+}
+
+int sspmm_set_kernel(int which) {
+    if (which < 0 || which > 3) {
+        set_error("kernel selector must be 0..3");
+        return (int)cudaErrorInvalidValue;
+    }
+    g_kernel_choice.store(which);
+    return 0;
+}
+
+int sspmm_device_status(int* status) {
+    g_err[0] = 0;
+    if (!status) return (int)cudaErrorInvalidValue;
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return fail(e, "device synchronize");
+    e = cudaMemcpyFromSymbol(status, g_device_status, sizeof(int));
+    if (e != cudaSuccess) return fail(e, "status read");
+    if (*status != 0) {
+        const int zero = 0;
+        e = cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int));
+        if (e != cudaSuccess) return fail(e, "status clear");
+    }
+    return 0;
+}
+
+int svc_begin(int M, int K, int vec_length, const int* d_csr_row_ptr, const int* d_csr_col_idx,
+              const void* d_csr_values_f16, void* stream, svc_job** job, int64_t* nvec) {
+    g_err[0] = 0;
+    if (!job || !nvec) { set_error("null output pointer"); return (int)cudaErrorInvalidValue; }
+    *job = nullptr;
+    if (vec_length != 8 && vec_length != 16) {
+        set_error("vec_length must be 8 or 16 (got %d)", vec_length);
+        return (int)cudaErrorInvalidValue;
+    }
+    if (M < 0 || K < 0) { set_error("negative dimension"); return (int)cudaErrorInvalidValue; }
+    if (K > kSvcMaxK) {
+        set_error("K = %d exceeds the supported maximum of %d columns", K, kSvcMaxK);
+        return (int)cudaErrorInvalidValue;
+    }
+    if (!d_csr_row_ptr || (M > 0 && !d_csr_col_idx && K > 0)) { set_error("null CSR pointer"); return (int)cudaErrorInvalidValue; }
+    svc_job* j = new (std::nothrow) svc_job();
+    if (!j) return (int)cudaErrorMemoryAllocation;
+    memset(j, 0, sizeof *j);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    j->stream = st;
+    cudaGetDevice(&j->device);
+    j->p.M = M; j->p.K = K; j->p.V = vec_length; j->p.m_vec = (M + vec_length - 1) / vec_length;
+    j->p.row_ptr = d_csr_row_ptr; j->p.col_idx = d_csr_col_idx;
+    j->p.vals = static_cast<const __half*>(d_csr_values_f16);
+    j->with_values = d_csr_values_f16 != nullptr;
+    const size_t mv = (size_t)j->p.m_vec;
+    // one allocation: vec_ptr[mv+1] | mode[mv] | tbl_len[mv] | pad | tbl_off[mv+1] | totals[2]
+    const size_t ints = (mv + 1) + mv + mv;
+    const size_t ints_padded = (ints + 3) & ~(size_t)3;
+    const size_t bytes = ints_padded * 4 + (mv + 1 + 2) * 8;
+    void* base = nullptr;
+    cudaError_t e = cudaMallocAsync(&base, bytes, st);
+    if (e != cudaSuccess) { delete j; return fail(e, "scratch allocation"); }
+    j->s.vec_ptr = static_cast<int*>(base);
+    j->s.mode = j->s.vec_ptr + mv + 1;
+    j->s.tbl_len = j->s.mode + mv;
+    j->s.tbl_off = reinterpret_cast<long long*>(static_cast<int*>(base) + ints_padded);
+    j->s.totals = j->s.tbl_off + mv + 1;
+    j->s.tables = nullptr;
+    e = svc_count_and_scan(j->p, j->s, j->with_values, st);
+    long long totals[2] = {0, 0};
+    if (e == cudaSuccess) e = cudaMemcpyAsync(totals, j->s.totals, sizeof totals, cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    int bad = 0;
+    if (e == cudaSuccess) e = svc_read_and_clear_bad_column_flag(&bad, st);
+    if (e != cudaSuccess || bad || totals[0] > 0x7fffffffLL) {
+        cudaFreeAsync(base, st);
+        delete j;
+        if (e != cudaSuccess) return fail(e, "SVC counting pass");
+        if (bad) set_error("CSR column id outside [0, K)");
+        else set_error("more than 2^31-1 vectors");
+        return (int)cudaErrorInvalidValue;
+    }
+    j->nvec = totals[0];
+    j->table_ints = totals[1];
+    *nvec = totals[0];
+    *job = j;
+    return 0;
+}
+
+int svc_finish(svc_job* j, int* d_vec_row_ptr, int* d_vec_col, void* d_vec_values_f16, void* stream) {
+    g_err[0] = 0;
+    if (!j || !d_vec_row_ptr || (j->nvec > 0 && !d_vec_col)) { set_error("null pointer"); return (int)cudaErrorInvalidValue; }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    cudaError_t e = cudaMemcpyAsync(d_vec_row_ptr, j->s.vec_ptr, ((size_t)j->p.m_vec + 1) * 4, cudaMemcpyDeviceToDevice, st);
+    if (e != cudaSuccess) return fail(e, "row pointer copy");
+    if (j->nvec == 0) return 0;
+    __half* ov = j->with_values ? static_cast<__half*>(d_vec_values_f16) : nullptr;
+    if (ov) {
+        e = cudaMemsetAsync(ov, 0, (size_t)j->nvec * j->p.V * sizeof(__half), st);
+        if (e != cudaSuccess) return fail(e, "value clear");
+    }
+    if (j->table_ints > 0 && !j->s.tables) {
+        e = cudaMallocAsync(reinterpret_cast<void**>(&j->s.tables), (size_t)j->table_ints * 4, st);
+        if (e != cudaSuccess) return fail(e, "table scratch allocation");
+    }
+    e = svc_emit(j->p, j->s, d_vec_col, ov, st);
+    if (e != cudaSuccess) return fail(e, "SVC emit");
+    j->stream = st;
+    return 0;
+}
+
+int svc_free(svc_job* j) {
+    if (!j) return 0;
+    if (j->s.tables) cudaFreeAsync(j->s.tables, j->stream);
+    if (j->s.vec_ptr) cudaFreeAsync(j->s.vec_ptr, j->stream);
+    delete j;
+    return 0;
+}
+
+int svc_replayed_rows(svc_job* j, int64_t* rows) {
+    g_err[0] = 0;
+    if (!j || !rows) return (int)cudaErrorInvalidValue;
+    const size_t mv = (size_t)j->p.m_vec;
+    *rows = 0;
+    if (mv == 0) return 0;
+    int* h = new (std::nothrow) int[mv];
+    if (!h) return (int)cudaErrorMemoryAllocation;
+    cudaError_t e = cudaMemcpyAsync(h, j->s.mode, mv * 4, cudaMemcpyDeviceToHost, j->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(j->stream);
+    if (e == cudaSuccess)
+        for (size_t i = 0; i < mv; ++i) *rows += h[i] != 0;
+    delete[] h;
+    return e == cudaSuccess ? 0 : fail(e, "mode read");
+}
+
+int sspmm_sorted_row_swizzle(int m_vec, const int* d_row_offsets, int* d_row_indices, void* stream) {
+    g_err[0] = 0;
+    if (m_vec < 0 || (m_vec > 0 && (!d_row_offsets || !d_row_indices))) {
+        set_error("bad argument");
+        return (int)cudaErrorInvalidValue;
+    }
+    if (m_vec == 0) return 0;
+    row_swizzle_kernel<<<(m_vec + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(m_vec, d_row_offsets,
+                                                                                          d_row_indices);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? 0 : fail(e, "row swizzle launch");
+}
+
+const char* sspmm_last_error_string(void) { return g_err; }
+const char* sspmm_version(void) { return "sspmm_b200 0.1 sm_100a"; }
+
+}  // extern "C"

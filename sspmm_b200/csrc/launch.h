@@ -1,0 +1,37 @@
+// Internal launcher interface shared by the kernel translation units and the C ABI.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+
+namespace sspmm_b200 {
+
+struct SpmmArgs {
+    int m_vec;                 // vector rows
+    int V;                     // rows per vector (8 or 16)
+    int N;                     // columns of the dense operand / of the output
+    int K;                     // rows of the dense operand
+    const int* row_indices;    // optional scheduling order of vector rows (may be null)
+    const int* row_offsets;    // [m_vec + 1]
+    const int* column_indices; // [nvec]
+    const __half* values;      // [nvec * V]
+    const __half* rhs;         // [K * N] row-major
+    void* out;                 // [m_vec * V * N] row-major, fp32 or fp16
+    bool out_f16;
+    // batching (one launch, grid z-less: tiles enumerate the batch too)
+    int batch;                 // >= 1
+    int64_t values_stride;     // elements between batches (0 = shared)
+    int64_t rhs_stride;
+    int64_t out_stride;
+    cudaStream_t stream;
+};
+
+// tcgen05 row-gather kernel.  Requires N % 8 == 0, 16-byte aligned rhs/values.
+cudaError_t launch_sspmm_gather(const SpmmArgs& a);
+// CUDA-core kernel without alignment requirements.
+cudaError_t launch_sspmm_simt(const SpmmArgs& a);
+
+// Records a message retrievable through sspmm_last_error_string().
+void set_error(const char* fmt, ...);
+
+}  // namespace sspmm_b200

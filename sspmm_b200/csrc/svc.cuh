@@ -1,0 +1,45 @@
+// Sparse vector compression (SVC) on the GPU: internal interface.
+//
+// Computes what the reference's CVSE.__init__ computes on the CPU
+// (RowMerge/sparse_matrix_format.py:94-123): vector row i covers matrix rows
+// V*i .. V*i+V-1; its column list is the union of those rows' column ids, in
+// the order CPython's  list(set(previous + row))  leaves them after V rebuilds.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace sspmm_b200 {
+
+// Largest K the bitmap kernels accept (bitmap of K bits + a 32-bit prefix per
+// word must fit one CTA's shared memory).
+constexpr int kSvcMaxK = 262144;
+
+struct SvcProblem {
+    int M, K, V, m_vec;
+    const int* row_ptr;   // [M+1]
+    const int* col_idx;   // [nnz]
+    const __half* vals;   // [nnz] or null
+};
+
+// Scratch owned by one compression.  Sizes in elements.
+struct SvcScratch {
+    int* vec_ptr;         // [m_vec+1]  counts, then exclusive scan = vector row pointers
+    int* mode;            // [m_vec]    0 = ascending order is exact, 1 = replay the hash table
+    int* tbl_len;         // [m_vec]    final table length of replayed groups (0 otherwise)
+    long long* tbl_off;   // [m_vec+1]  exclusive scan of per-group table scratch
+    long long* totals;    // [2]        {nvec, table scratch ints}
+    int* tables;          // [totals[1]] allocated after the counting pass
+};
+
+size_t svc_table_ints_per_len(bool with_values);  // scratch ints per unit of tbl_len, as a fraction x4
+
+// Pass 1: per-group distinct counts, mode decision, scans.  Asynchronous on `stream`.
+cudaError_t svc_count_and_scan(const SvcProblem& p, const SvcScratch& s, bool with_values, cudaStream_t stream);
+// Pass 2: emits column lists (and value vectors when out_vals != null; out_vals must be zero-filled).
+cudaError_t svc_emit(const SvcProblem& p, const SvcScratch& s, int* out_col, __half* out_vals, cudaStream_t stream);
+
+// Device flag set when a column id outside [0, K) was met (such entries are skipped).
+cudaError_t svc_read_and_clear_bad_column_flag(int* flag, cudaStream_t stream);
+
+}  // namespace sspmm_b200

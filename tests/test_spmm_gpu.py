@@ -1,0 +1,172 @@
+"""GPU parity tests of the vector-sparse SpMM, called through the C ABI, against
+the CPU oracle (fp32 restatement of the reference's host loop).
+
+Tolerance: |gpu - oracle| <= 1e-2 * max(|oracle|, eps_row) with eps_row = 1e-3 *
+the largest magnitude in that output row (outputs near zero are common with
+N(0, 0.02) weights).  fp32 output normally agrees to ~1e-5; the bound is the
+north-star's."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import ref_kernel, spmm_oracle, svc_oracle
+from sspmm_b200 import ops, synthetic
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def compress(a, V):
+    r = svc_oracle.cvse(a.M, a.K, a.nnz, a.row_lists(), V)
+    vals = svc_oracle.pack_values(a.M, V, a.row_ptr, a.col_idx, a.values, r)
+    return (np.asarray(r.vec_row_ptr, dtype=np.int32), np.asarray(r.vec_colInd_list, dtype=np.int32), vals)
+
+
+def assert_close(got, ref, rel=1e-2):
+    got = np.asarray(got, dtype=np.float64)
+    ref = np.asarray(ref, dtype=np.float64)
+    assert got.shape == ref.shape
+    assert np.isfinite(got).all()
+    floor = 1e-3 * np.max(np.abs(ref), axis=1, keepdims=True) + 1e-30
+    err = np.abs(got - ref) / np.maximum(np.abs(ref), floor)
+    assert err.max() <= rel, f"max rel err {err.max():.3e} at {np.unravel_index(err.argmax(), err.shape)}"
+
+
+def gpu_spmm(ptr, col, vals, rhs, V, out_dtype, row_indices=None, kernel=ops.KERNEL_AUTO):
+    ops.set_kernel(kernel)
+    try:
+        out = ops.sspmm(torch.from_numpy(ptr).to(DEV), torch.from_numpy(col).to(DEV), torch.from_numpy(vals).to(DEV),
+                        torch.from_numpy(rhs).to(DEV), V, row_indices=row_indices, out_dtype=out_dtype)
+        torch.cuda.synchronize()
+    finally:
+        ops.set_kernel(ops.KERNEL_AUTO)
+    assert ops.device_status() == 0
+    return out.float().cpu().numpy()
+
+
+@pytest.mark.parametrize("kernel", [ops.KERNEL_GATHER, ops.KERNEL_SIMT])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.float16])
+@pytest.mark.parametrize("V", [8, 16])
+def test_config1(lib, V, out_dtype, kernel):
+    a, rhs = synthetic.config1()
+    ptr, col, vals = compress(a, V)
+    ref = spmm_oracle.sspmm_host(V, ptr, col, vals, rhs)
+    got = gpu_spmm(ptr, col, vals, rhs, V, out_dtype, kernel=kernel)
+    assert_close(got, ref, rel=1e-2 if out_dtype == torch.float16 else 1e-3)
+
+
+@pytest.mark.parametrize("shape_id,sparsity_id", [(0, 0), (0, 3), (0, 5), (1, 1), (1, 3), (1, 5)])
+def test_ffn_v16(lib, shape_id, sparsity_id):
+    a, rhs = synthetic.ffn(shape_id, sparsity_id)
+    ptr, col, vals = compress(a, 16)
+    ref = spmm_oracle.sspmm_host(16, ptr, col, vals, rhs, threads=8)
+    assert_close(gpu_spmm(ptr, col, vals, rhs, 16, torch.float16, kernel=ops.KERNEL_GATHER), ref)
+    assert_close(gpu_spmm(ptr, col, vals, rhs, 16, torch.float32, kernel=ops.KERNEL_GATHER), ref, rel=1e-3)
+
+
+def random_cvse(rng, m_vec, K, V, lens):
+    ptr = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    col = np.concatenate([rng.permutation(K)[:l] for l in lens] + [np.zeros(0, dtype=np.int64)]).astype(np.int32)
+    vals = rng.uniform(-1, 1, int(ptr[-1]) * V).astype(np.float16)
+    return ptr, col, vals
+
+
+@pytest.mark.parametrize("V", [8, 16])
+@pytest.mark.parametrize("N", [8, 64, 72, 128, 136, 200, 256, 384])
+def test_ragged_rows_and_column_tails(lib, V, N):
+    """Vector rows of every residue class around the 16/64-vector steps, empty
+    rows, and N with partial 128-column tiles."""
+    rng = np.random.default_rng(100 + N + V)
+    lens = [0, 1, 2, 3, 4, 5, 15, 16, 17, 31, 32, 33, 47, 48, 49, 63, 64, 65, 0, 127, 128, 129, 200, 0]
+    K = 300
+    ptr, col, vals = random_cvse(rng, len(lens), K, V, lens)
+    rhs = rng.normal(0, 1, (K, N)).astype(np.float16)
+    ref = spmm_oracle.sspmm_host(V, ptr, col, vals, rhs)
+    assert_close(gpu_spmm(ptr, col, vals, rhs, V, torch.float32, kernel=ops.KERNEL_GATHER), ref, rel=1e-3)
+    assert_close(gpu_spmm(ptr, col, vals, rhs, V, torch.float16, kernel=ops.KERNEL_GATHER), ref)
+
+
+@pytest.mark.parametrize("V", [8, 16])
+def test_unaligned_n_uses_cuda_core_path(lib, V):
+    rng = np.random.default_rng(7)
+    lens = [5, 0, 40, 17]
+    ptr, col, vals = random_cvse(rng, len(lens), 64, V, lens)
+    rhs = rng.normal(0, 1, (64, 50)).astype(np.float16)          # 50 % 8 != 0
+    ref = spmm_oracle.sspmm_host(V, ptr, col, vals, rhs)
+    assert_close(gpu_spmm(ptr, col, vals, rhs, V, torch.float32), ref, rel=1e-3)
+
+
+def test_output_is_fully_overwritten(lib):
+    rng = np.random.default_rng(8)
+    lens = [0, 3, 0, 0]
+    ptr, col, vals = random_cvse(rng, 4, 32, 8, lens)
+    rhs = rng.normal(0, 1, (32, 128)).astype(np.float16)
+    out = torch.full((32, 128), float("nan"), dtype=torch.float16, device=DEV)
+    ops.sspmm(torch.from_numpy(ptr).to(DEV), torch.from_numpy(col).to(DEV), torch.from_numpy(vals).to(DEV),
+              torch.from_numpy(rhs).to(DEV), 8, out=out)
+    torch.cuda.synchronize()
+    got = out.float().cpu().numpy()
+    assert np.isfinite(got).all()
+    assert not got[0:8].any() and not got[16:].any()
+
+
+def test_row_swizzle_does_not_change_result(lib):
+    a = synthetic.power_law(4096, np.random.default_rng(11))
+    ptr, col, vals = compress(a, 8)
+    rhs = np.random.default_rng(12).normal(0, 1, (a.K, 128)).astype(np.float16)
+    base = gpu_spmm(ptr, col, vals, rhs, 8, torch.float32)
+    swz = ops.sorted_row_swizzle(torch.from_numpy(ptr).to(DEV))
+    got = gpu_spmm(ptr, col, vals, rhs, 8, torch.float32, row_indices=swz)
+    assert np.array_equal(base, got)
+    ref = spmm_oracle.sspmm_host(8, ptr, col, vals, rhs, threads=8)
+    assert_close(got, ref, rel=1e-3)
+
+
+def test_power_law_sweep_sample(lib):
+    a = synthetic.sweep_matrix(3)
+    ptr, col, vals = compress(a, 8)
+    rhs = np.random.default_rng(13).normal(0, 1, (a.K, 128)).astype(np.float16)
+    ref = spmm_oracle.sspmm_host(8, ptr, col, vals, rhs, threads=8)
+    assert_close(gpu_spmm(ptr, col, vals, rhs, 8, torch.float16), ref)
+
+
+def test_conv_layer_full_width_properties(lib):
+    """Conv config at its full N = 25088: linearity in B and agreement with the
+    oracle on a sample of vector rows (the full CPU product would take minutes)."""
+    a = synthetic.conv_weight(1, 1)      # 128 x 1152 at 0.9
+    V = 16
+    ptr, col, vals = compress(a, V)
+    rng = np.random.default_rng(14)
+    N = synthetic.CONV_N
+    b1 = rng.normal(0, 1, (a.K, N)).astype(np.float16)
+    got = gpu_spmm(ptr, col, vals, b1, V, torch.float32)
+    rows = (2, 4)
+    ref = spmm_oracle.sspmm_host(V, ptr, col, vals, b1, rows=rows, threads=8)
+    assert_close(got[rows[0] * V: rows[1] * V], ref, rel=1e-3)
+    # linearity: A(2*b1) == 2*A(b1) exactly in fp32 (power-of-two scaling)
+    got2 = gpu_spmm(ptr, col, vals, (b1 * np.float16(2)).astype(np.float16), V, torch.float32)
+    assert np.array_equal(got2, 2 * got)
+
+
+@pytest.mark.skipif(not ref_kernel.available(), reason="reference kernel library not built")
+@pytest.mark.parametrize("V", [8, 16])
+def test_against_reference_gpu_kernel(lib, V):
+    """The reference's own kernel (compiled unmodified from its sources) on the
+    same inputs: pins the oracle's reading of the operand layout."""
+    a, rhs = synthetic.config1()
+    ptr, col, vals = compress(a, V)
+    pad = ref_kernel.PAD_VECTORS
+    d_ptr = torch.from_numpy(ptr).to(DEV)
+    d_col = torch.cat([torch.from_numpy(col), torch.zeros(pad, dtype=torch.int32)]).to(DEV)
+    d_val = torch.cat([torch.from_numpy(vals), torch.zeros(pad * V, dtype=torch.float16)]).to(DEV)
+    d_rhs = torch.from_numpy(rhs).to(DEV)
+    m_vec = ptr.size - 1
+    idx = torch.arange(m_vec, dtype=torch.int32, device=DEV)
+    out = torch.zeros((m_vec * V, rhs.shape[1]), dtype=torch.float32, device=DEV)
+    torch.cuda.synchronize()
+    rc = ref_kernel.sspmm_ref(m_vec, V, rhs.shape[1], a.K, idx, d_ptr, d_col, d_val, d_rhs, out)
+    torch.cuda.synchronize()
+    assert rc == 0
+    ref = spmm_oracle.sspmm_host(V, ptr, col, vals, rhs)
+    assert_close(out.cpu().numpy(), ref, rel=1e-3)
+    assert_close(gpu_spmm(ptr, col, vals, rhs, V, torch.float32), out.cpu().numpy(), rel=1e-3)

@@ -1,0 +1,149 @@
+"""GPU parity tests of sparse vector compression: the CUDA path, called through
+the C ABI, against the golden vectors of the unmodified reference module and
+against the CPU oracle on seeded inputs.  Integer outputs must be bit-exact."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import svc_oracle
+from sspmm_b200 import ops, synthetic
+from tests.golden_cases import golden_cases, load_golden
+
+pytestmark = pytest.mark.gpu
+
+CASES = golden_cases()
+GOLD = load_golden()
+
+
+def run_gpu(a, V, with_values=True):
+    dev = torch.device("cuda:0")
+    ptr = torch.from_numpy(a.row_ptr).to(dev)
+    col = torch.from_numpy(a.col_idx).to(dev)
+    val = torch.from_numpy(a.values).to(dev) if with_values else None
+    vec_ptr, vec_col, vec_val, replayed = ops.svc(ptr, col, val, a.M, a.K, V)
+    torch.cuda.synchronize()
+    return (vec_ptr.cpu().numpy(), vec_col.cpu().numpy(), None if vec_val is None else vec_val.cpu().numpy(), replayed)
+
+
+def check_against_oracle(a, V):
+    r = svc_oracle.cvse(a.M, a.K, a.nnz, a.row_lists(), V)
+    ptr, col, val, _ = run_gpu(a, V)
+    assert np.array_equal(ptr, np.asarray(r.vec_row_ptr, dtype=np.int32))
+    assert np.array_equal(col, np.asarray(r.vec_colInd_list, dtype=np.int32))
+    exp = svc_oracle.pack_values(a.M, V, a.row_ptr, a.col_idx, a.values, r)
+    assert np.array_equal(val.view(np.uint16), exp.view(np.uint16))
+    return r
+
+
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_svc_matches_reference_golden(lib, name):
+    a, V = CASES[name]
+    ptr, col, val, replayed = run_gpu(a, V)
+    assert np.array_equal(ptr, GOLD[name + "/vec_row_ptr"])
+    assert np.array_equal(col, GOLD[name + "/vec_colInd_list"])
+    # value vectors: densifying the compressed form gives back A
+    dense = svc_oracle.densify(ptr.size - 1, V, a.K, ptr.tolist(), col.tolist(), val)
+    assert np.array_equal(dense[: a.M].view(np.uint16), a.dense().view(np.uint16))
+    assert not dense[a.M:].any()
+    if name.startswith("powerlaw"):
+        assert replayed > 0          # the hash-order replay really ran
+
+
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_python_entry_point_matches_reference_golden(lib, name):
+    from sspmm_b200 import sparse_matrix_format as smf
+    a, V = CASES[name]
+    c = smf.CVSE(a.M, a.K, a.nnz, a.row_lists(), V)
+    assert c.vec_row_ptr == GOLD[name + "/vec_row_ptr"].tolist()
+    assert c.vec_colInd_list == GOLD[name + "/vec_colInd_list"].tolist()
+    assert c.tile_num == GOLD[name + "/tile_num"].tolist()
+    assert [c.return_CSR_storage(), c.return_CVSE_storage(), c.return_TCF_storage(),
+            c.return_SRBCSR_storage()] == GOLD[name + "/storage"].tolist()
+    assert c.num_vec == len(c.vec_colInd_list) and len(c.vec_colInd_list_array) == c.num_vec_row
+
+
+@pytest.mark.parametrize("V", [8, 16])
+@pytest.mark.parametrize("shape_id,sparsity_id", [(0, 0), (0, 5), (1, 2), (1, 4)])
+def test_svc_ffn_configs(lib, V, shape_id, sparsity_id):
+    a, _ = synthetic.ffn(shape_id, sparsity_id)
+    check_against_oracle(a, V)
+
+
+def test_svc_power_law_with_giant_rows(lib):
+    a = synthetic.power_law(16384, np.random.default_rng(123))
+    r = check_against_oracle(a, 8)
+    assert max(len(l) for l in r.vec_colInd_list_array) > 1229     # a table of 8192 slots or more was replayed
+
+
+@pytest.mark.parametrize("V", [8, 16])
+def test_svc_edge_cases(lib, V):
+    rng = np.random.default_rng(V)
+    cases = []
+    # empty matrix rows everywhere
+    cases.append(synthetic.CSR(40, 100, np.zeros(41, dtype=np.int32), np.zeros(0, dtype=np.int32), np.zeros(0, dtype=np.float16)))
+    # single row, single entry, last column
+    cases.append(synthetic.CSR(1, 70000, np.array([0, 1], dtype=np.int32), np.array([69999], dtype=np.int32), np.array([1.5], dtype=np.float16)))
+    # M = 0
+    cases.append(synthetic.CSR(0, 10, np.zeros(1, dtype=np.int32), np.zeros(0, dtype=np.int32), np.zeros(0, dtype=np.float16)))
+    # dense rows (every column), M not a multiple of V
+    M, K = 19, 96
+    ptr = (np.arange(M + 1) * K).astype(np.int32)
+    cases.append(synthetic.CSR(M, K, ptr, np.tile(np.arange(K, dtype=np.int32), M), rng.uniform(-1, 1, M * K).astype(np.float16)))
+    # exactly at the growth thresholds of the hash table: 4, 5, 18, 19, 76, 77, 306, 307 distinct keys, wide key range
+    for u in (4, 5, 18, 19, 76, 77, 306, 307, 1228, 1229):
+        cols = rng.permutation(200000)[:u].astype(np.int32)
+        cases.append(synthetic.CSR(1, 200000, np.array([0, u], dtype=np.int32), cols, rng.uniform(-1, 1, u).astype(np.float16)))
+    # colliding keys: all congruent modulo every small table length
+    cols = (np.arange(30, dtype=np.int32) * 8192 + 5)
+    lens = [10, 0, 8, 12] + [0] * (V - 4)
+    ptr = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    cases.append(synthetic.CSR(V, 30 * 8192, ptr, rng.permutation(cols).astype(np.int32), rng.uniform(-1, 1, 30).astype(np.float16)))
+    for a in cases:
+        check_against_oracle(a, V)
+
+
+def test_svc_rejects_bad_column(lib):
+    a = synthetic.CSR(2, 10, np.array([0, 1, 2], dtype=np.int32), np.array([3, 10], dtype=np.int32), np.ones(2, dtype=np.float16))
+    from sspmm_b200 import capi
+    with pytest.raises(capi.SspmmError):
+        run_gpu(a, 8)
+    # the library stays usable afterwards
+    ok = synthetic.CSR(2, 10, np.array([0, 1, 2], dtype=np.int32), np.array([3, 9], dtype=np.int32), np.ones(2, dtype=np.float16))
+    check_against_oracle(ok, 8)
+
+
+def test_all_zero_vector_count_entry_point(lib):
+    from sspmm_b200 import sparse_matrix_format as smf
+    a, V = CASES["config1_v8"]
+    om = smf.OriginMatrix(a.M, a.K, a.row_ptr, a.col_idx)
+    assert smf.return_all_zero_vec(V, a.M, a.K, om) == int(GOLD["config1_v8/all_zero_vec_cnt"][0])
+
+
+def test_sorted_row_swizzle(lib):
+    a = synthetic.power_law(4096, np.random.default_rng(5))
+    r = svc_oracle.cvse(a.M, a.K, a.nnz, a.row_lists(), 8)
+    d = torch.tensor(r.vec_row_ptr, dtype=torch.int32, device="cuda:0")
+    got = ops.sorted_row_swizzle(d).cpu().numpy()
+    assert np.array_equal(got, svc_oracle.sorted_row_swizzle(r.vec_row_ptr))
+
+
+def test_svc_full_size_properties(lib):
+    """n = 65536 power-law matrix (largest sweep size): checked through
+    size-independent properties instead of the slow CPU oracle."""
+    a = synthetic.power_law(65536, np.random.default_rng(2024))
+    V = 8
+    ptr, col, val, _ = run_gpu(a, V)
+    m_vec = a.M // V
+    assert ptr[0] == 0 and np.all(np.diff(ptr) >= 0) and ptr[-1] == col.size
+    # each vector row holds exactly the distinct columns of its V rows
+    grp = np.repeat(np.arange(a.M) // V, np.diff(a.row_ptr)).astype(np.int64)
+    key_in = np.unique(grp * a.K + a.col_idx)
+    key_out = np.repeat(np.arange(m_vec, dtype=np.int64), np.diff(ptr)) * a.K + col
+    assert key_out.size == key_in.size and np.array_equal(np.sort(key_out), key_in)
+    # value vectors carry every original value once and zeros elsewhere
+    assert np.isclose(val.astype(np.float64).sum(), a.values.astype(np.float64).sum(), atol=1e-6)
+    assert np.count_nonzero(val) == np.count_nonzero(a.values)
+    # spot-check a slice of vector rows against the oracle, including order
+    sub = synthetic.CSR(512, a.K, (a.row_ptr[:513] - a.row_ptr[0]).astype(np.int32), a.col_idx[a.row_ptr[0]:a.row_ptr[512]], a.values[a.row_ptr[0]:a.row_ptr[512]])
+    r = svc_oracle.cvse(sub.M, sub.K, sub.nnz, sub.row_lists(), V)
+    assert np.array_equal(col[: ptr[64]], np.asarray(r.vec_colInd_list, dtype=np.int32))
