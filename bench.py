@@ -1,0 +1,470 @@
+"""Benchmark of the SVC -> vector-sparse SpMM path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (the configuration the multi-GPU metric is quoted on): the conv-as-GEMM
+set -- 8 pruned conv layers x sparsity {0.8, 0.9} x V {8, 16} = 32 products
+C = A_vs * B with B = K x 25088 fp16 N(0,1), B and C sharded along N over the
+ranks (strong scaling, no collective on the data path).  One step = all 32
+products once.  The weights are compressed by the GPU SVC before timing.
+
+One JSON line on stdout (rank 0).  `value` = useful TFLOP/s = 2*nnz*N_total summed
+over the 32 products / device time of a step, operands resident in HBM; `e2e` =
+the same with B coming from pinned host memory and C going back every step.
+`--impl reference` times the reference's CPU path (restated in oracle/) on the
+host cores, on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from sspmm_b200 import synthetic  # noqa: E402
+
+METRIC = "useful_tflops_2nnzN"
+UNIT = "TFLOP/s"
+WORKLOAD = ("conv-as-GEMM pruned weights: 8 layers (Cout,K) in %s x sparsity {0.8,0.9} x V {8,16}, "
+            "B = K x 25088 fp16 N(0,1), sharded along N" % (synthetic.CONV_LAYERS,))
+
+
+def conv_problems():
+    """(layer_id, sparsity_id, V) for the 32 products, ordered so that products
+    sharing a layer are far apart within a step."""
+    return [(l, s, V) for s in range(len(synthetic.CONV_SPARSITIES)) for V in (8, 16)
+            for l in range(len(synthetic.CONV_LAYERS))]
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": d["hbm_gbs"], "tensor_tflops": d.get("bf16_tflops_sustained", d["bf16_tflops"]),
+                "tensor_tflops_burst": d["bf16_tflops"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "tensor_tflops": 1400.0, "tensor_tflops_burst": 1590.0, "source": "fallback"}
+
+
+# --------------------------------------------------------------------------- #
+# clocks
+# --------------------------------------------------------------------------- #
+
+class ClockSampler:
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for ln in open(self.path):
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.path)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------- #
+# reference arm / CPU baseline (the only users of oracle/ in this file)
+# --------------------------------------------------------------------------- #
+
+def cpu_sample(n_cols: int = synthetic.CONV_N, target_rows: int = 32):
+    """A bounded sample of the workload for the CPU: layer (512, 4608) at
+    sparsity 0.9, V=16: the SVC of the whole layer, and the host SpMM on
+    `target_rows` vector rows and `n_cols` columns of B."""
+    from oracle import spmm_oracle, svc_oracle
+    a = synthetic.conv_weight(3, 1)
+    V = 16
+    rows = a.row_lists()
+    t0 = time.perf_counter()
+    r = svc_oracle.cvse(a.M, a.K, a.nnz, rows, V)
+    t_svc = time.perf_counter() - t0
+    vals = svc_oracle.pack_values(a.M, V, a.row_ptr, a.col_idx, a.values, r)
+    rng = np.random.default_rng(0)
+    rhs = rng.normal(0, 1, (a.K, n_cols)).astype(np.float16)
+    cores = os.cpu_count() or 1
+    nrows = min(target_rows, r.num_vec_row)
+    spmm_oracle.sspmm_host(V, r.vec_row_ptr, r.vec_colInd_list, vals, rhs, rows=(0, 1), threads=cores)  # warm
+    t0 = time.perf_counter()
+    spmm_oracle.sspmm_host(V, r.vec_row_ptr, r.vec_colInd_list, vals, rhs, rows=(0, nrows), threads=cores)
+    t_spmm = time.perf_counter() - t0
+    nnz_sample = int(a.row_ptr[nrows * V] - a.row_ptr[0])
+    useful = 2.0 * nnz_sample * n_cols
+    return {"svc_s": t_svc, "spmm_s": t_spmm, "useful_flops": useful, "cores": cores,
+            "sample": f"layer (512,4608) s=0.9 V=16: SVC of the whole layer (1 core, CPython) + host fp32 SpMM on "
+                      f"{nrows} of {r.num_vec_row} vector rows x {n_cols} of 25088 columns ({cores} OpenMP threads)"}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    for _ in range(args.warmup):
+        cpu_sample(n_cols=128, target_rows=2)
+    t_all, flops_all, last = 0.0, 0.0, None
+    for _ in range(args.steps):
+        last = cpu_sample()
+        t_all += last["spmm_s"]
+        flops_all += last["useful_flops"]
+    val = flops_all / t_all / 1e12
+    line = {"impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": 1e3 * t_all / args.steps, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "sample": last["sample"]},
+            "cpu_baseline": {"value": val, "unit": UNIT, "cores": last["cores"], "kind": "port",
+                             "sample": last["sample"], "svc_seconds_per_matrix": last["svc_s"]},
+            "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+# --------------------------------------------------------------------------- #
+# our arm
+# --------------------------------------------------------------------------- #
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    from sspmm_b200 import build, capi, ops, parallel
+    build.build()
+    capi.lib()
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+
+    N_total = synthetic.CONV_N
+    n0, n1 = parallel.shard_bounds(N_total, world)[rank]
+    n_loc = n1 - n0
+    peaks = load_peaks()
+
+    # ---- operands: weights compressed on the GPU, one B and C per product
+    probs = []
+    g = torch.Generator(device=dev)
+    g.manual_seed(1234 + rank)
+    cache = {}
+    todo = conv_problems()
+    if args.only:
+        todo = [tuple(int(x) for x in args.only.split(","))]
+    for (l, s, V) in todo:
+        if (l, s) not in cache:
+            cache[(l, s)] = synthetic.conv_weight(l, s)
+        a = cache[(l, s)]
+        d_ptr = torch.from_numpy(a.row_ptr).to(dev)
+        d_col = torch.from_numpy(a.col_idx).to(dev)
+        d_val = torch.from_numpy(a.values).to(dev)
+        vp, vc, vv, _ = ops.svc(d_ptr, d_col, d_val, a.M, a.K, V)
+        m_vec = vp.numel() - 1
+        nvec = vc.numel()
+        B = torch.randn((a.K, n_loc), generator=g, device=dev, dtype=torch.float16)
+        C = torch.empty((m_vec * V, n_loc), device=dev, dtype=torch.float16)
+        k_used = int(torch.unique(vc).numel())
+        probs.append(dict(l=l, s=s, V=V, M=a.M, K=a.K, nnz=a.nnz, m_vec=m_vec, nvec=nvec, k_used=k_used,
+                          vp=vp, vc=vc, vv=vv, B=B, C=C))
+    useful_flops_total = sum(2.0 * p["nnz"] * N_total for p in probs)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def launch(p):
+        ops.sspmm(p["vp"], p["vc"], p["vv"], p["B"], p["V"], out=p["C"])
+
+    def step(evs=None):
+        for i, p in enumerate(probs):
+            if evs is not None:
+                evs[i][0].record()
+            launch(p)
+            if evs is not None:
+                evs[i][1].record()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    assert ops.device_status() == 0
+
+    # ---- timed region: K steps, per-step and per-launch CUDA events on the launching stream
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    step_evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    launch_evs = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in probs]
+                  for _ in range(args.steps)]
+    barrier()
+    wall0 = time.perf_counter()
+    for k in range(args.steps):
+        flush.zero_()                       # evicts L2 between steps (outside the step's events)
+        step_evs[k][0].record()
+        step(launch_evs[k])
+        step_evs[k][1].record()
+    barrier()
+    wall = time.perf_counter() - wall0
+    clocks = sampler.stop() if rank == 0 else None
+    step_ms = [a.elapsed_time(b) for a, b in step_evs]
+    total_ms = float(sum(step_ms))
+    if world > 1:
+        t = torch.tensor([total_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms = float(t.item())
+    ms_per_step = total_ms / args.steps
+    value = useful_flops_total / (ms_per_step * 1e-3) / 1e12
+
+    # ---- roofline of the dominant kernel, from the per-launch events of this rank
+    launch_ms = np.array([[a.elapsed_time(b) for a, b in row] for row in launch_evs])     # [steps, 32]
+    per_prob_ms = launch_ms.mean(axis=0)
+    f_alg = np.array([2.0 * p["nvec"] * p["V"] * n_loc for p in probs])
+    b_alg = np.array([2.0 * p["V"] * p["nvec"] + 4.0 * p["nvec"] + 4.0 * (p["m_vec"] + 1) + 2.0 * p["k_used"] * n_loc
+                      + 2.0 * p["m_vec"] * p["V"] * n_loc for p in probs])
+    t_tensor = f_alg / (peaks["tensor_tflops"] * 1e12)
+    t_hbm = b_alg / (peaks["hbm_gbs"] * 1e9)
+    t_bound = np.maximum(t_tensor, t_hbm)
+    kernel_s = per_prob_ms.sum() * 1e-3
+    tensor_bound = bool(t_tensor.sum() >= t_hbm.sum())
+    if tensor_bound:
+        achieved = f_alg.sum() / kernel_s / 1e12
+        roof = {"bound": "tensor", "achieved": achieved, "peak": peaks["tensor_tflops"], "unit": "TFLOP/s",
+                "frac": achieved / peaks["tensor_tflops"]}
+    else:
+        achieved = b_alg.sum() / kernel_s / 1e9
+        roof = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                "frac": achieved / peaks["hbm_gbs"]}
+    roof.update({"traffic": None, "peak_source": peaks["source"] + (" sustained bf16" if tensor_bound else " copy"),
+                 "kernel": "sspmm_gather_kernel", "t_bound_over_t": float(t_bound.sum() / kernel_s),
+                 "algorithmic_flops_per_step": float(f_alg.sum()), "algorithmic_bytes_per_step": float(b_alg.sum()),
+                 "kernel_ms_per_step": float(per_prob_ms.sum())})
+    traffic_file = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(traffic_file):
+        try:
+            roof["traffic"] = json.load(open(traffic_file)).get("conv_step_dram_bytes")
+        except Exception:
+            pass
+
+    # ---- end to end: B from pinned host memory, C back to the host, every step
+    e2e = None
+    e2e_steps = min(args.steps, 2)
+    hostB = {}
+    for p in probs:
+        if p["K"] not in hostB:
+            hostB[p["K"]] = torch.randn((p["K"], n_loc), dtype=torch.float16).pin_memory()
+    hostC = {}
+    for p in probs:
+        key = p["m_vec"] * p["V"]
+        if key not in hostC:
+            hostC[key] = torch.empty((key, n_loc), dtype=torch.float16).pin_memory()
+    h2d = sum(p["K"] * n_loc * 2 for p in probs)
+    d2h = sum(p["m_vec"] * p["V"] * n_loc * 2 for p in probs)
+
+    def e2e_step():
+        for p in probs:
+            p["B"].copy_(hostB[p["K"]], non_blocking=True)
+            launch(p)
+            hostC[p["m_vec"] * p["V"]].copy_(p["C"], non_blocking=True)
+
+    e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e = {"value": useful_flops_total / (e2e_ms / e2e_steps * 1e-3) / 1e12, "unit": UNIT,
+           "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h), "steps": e2e_steps,
+           "ms_per_step": e2e_ms / e2e_steps}
+    del hostB, hostC
+
+    extras = {}
+    if rank == 0:
+        # ---- same-shape dense fp16 GEMM from the vendor library, for comparison only
+        dense_ms = {}
+        for p in probs:
+            key = (p["m_vec"] * p["V"], p["K"])
+            if key in dense_ms:
+                continue
+            A = torch.randn(key, device=dev, dtype=torch.float16)
+            for _ in range(2):
+                torch.matmul(A, p["B"])
+            a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a0.record()
+            for _ in range(5):
+                torch.matmul(A, p["B"])
+            a1.record()
+            torch.cuda.synchronize()
+            dense_ms[key] = a0.elapsed_time(a1) / 5
+        dense_total = sum(dense_ms[(p["m_vec"] * p["V"], p["K"])] for p in probs)
+        extras["comparators"] = {"cublas_dense_fp16": {
+            "ms_per_step": dense_total, "useful_tflops": 2.0 * sum(p["nnz"] for p in probs) * n_loc / dense_total / 1e9,
+            "dense_tflops": sum(2.0 * p["m_vec"] * p["V"] * p["K"] * n_loc for p in probs) / dense_total / 1e9,
+            "note": "torch.matmul (cuBLAS) on a dense M'xK matrix of the same shape, this rank's columns"}}
+        extras["per_product"] = [
+            {"layer": list(synthetic.CONV_LAYERS[p["l"]]), "sparsity": synthetic.CONV_SPARSITIES[p["s"]], "V": p["V"],
+             "nvec": p["nvec"], "padding": p["nvec"] * p["V"] / p["nnz"], "us": float(per_prob_ms[i] * 1e3),
+             "useful_tflops": 2.0 * p["nnz"] * n_loc / per_prob_ms[i] / 1e9,
+             "vector_dense_tflops": float(f_alg[i] / per_prob_ms[i] / 1e9),
+             "dense_equiv_tflops": 2.0 * p["M"] * p["K"] * n_loc / per_prob_ms[i] / 1e9,
+             "gbs": float(b_alg[i] / per_prob_ms[i] / 1e6), "roofline_frac": float(t_bound[i] / (per_prob_ms[i] * 1e-3))}
+            for i, p in enumerate(probs)]
+        if not args.no_extras:
+            extras["svc"] = bench_svc(torch, ops, dev)
+            extras["ffn"] = bench_ffn(torch, ops, dev, peaks)
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        s = cpu_sample()
+        cpu = {"value": s["useful_flops"] / s["spmm_s"] / 1e12, "unit": UNIT, "cores": s["cores"], "kind": "port",
+               "sample": s["sample"], "svc_seconds_per_matrix": s["svc_s"]}
+
+    if rank == 0:
+        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+                "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+                "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+                "config": {"workload": WORKLOAD if not args.only else "single product " + args.only, "N_total": N_total, "N_per_gpu": n_loc, "products_per_step": len(probs),
+                           "l2": "operands of a step exceed L2 and a 256 MiB buffer is written between steps",
+                           "parallelism": f"B and C column-sharded over {world} GPU(s), A_vs replicated, no collective"},
+                "roofline": roof, "cpu_baseline": cpu, "e2e": e2e,
+                "gpu_launches": len(probs) * args.steps * kernels_per_product(), "clocks": clocks,
+                "wall_s_timed_region": wall}
+        line.update(extras)
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def kernels_per_product() -> int:
+    return 1
+
+
+def bench_svc(torch, ops, dev, ids=(0, 1, 2)):
+    """SVC throughput on a sample of the power-law sweep (V=8): device-resident,
+    through the host-buffer entry point, and the CPU oracle on one core."""
+    from oracle import svc_oracle
+    from sspmm_b200 import sparse_matrix_format as smf
+    mats = [synthetic.sweep_matrix(i) for i in ids]
+    dmats = [(torch.from_numpy(a.row_ptr).to(dev), torch.from_numpy(a.col_idx).to(dev), torch.from_numpy(a.values).to(dev), a)
+             for a in mats]
+    for p, c, v, a in dmats:
+        ops.svc(p, c, v, a.M, a.K, 8)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    nbytes = 0
+    for p, c, v, a in dmats:
+        vp, vc, vv, _ = ops.svc(p, c, v, a.M, a.K, 8)
+        nbytes += 4 * (a.M + 1) + 6 * a.nnz + 4 * vp.numel() + 4 * vc.numel() + 2 * vv.numel()
+    torch.cuda.synchronize()
+    t_dev = time.perf_counter() - t0
+    t0 = time.perf_counter()
+    for a in mats:
+        smf.CVSE(a.M, a.K, a.nnz, a.row_lists(), 8)
+    t_host_api = time.perf_counter() - t0
+    t0 = time.perf_counter()
+    for a in mats:
+        svc_oracle.cvse(a.M, a.K, a.nnz, a.row_lists(), 8)
+    t_cpu = time.perf_counter() - t0
+    return {"sample": f"sweep matrices {list(ids)} (n = {[a.M for a in mats]}), V=8",
+            "device_matrices_per_s": len(mats) / t_dev, "device_gbs": nbytes / t_dev / 1e9,
+            "python_entry_point_matrices_per_s": len(mats) / t_host_api,
+            "cpu_oracle_matrices_per_s_1core": len(mats) / t_cpu, "speedup_device_vs_cpu": t_cpu / t_dev}
+
+
+def bench_ffn(torch, ops, dev, peaks):
+    """FFN configuration (V=16, N=256): single-call latency per matrix."""
+    out = []
+    for shape_id in range(2):
+        for sid in range(len(synthetic.FFN_SPARSITIES)):
+            a, rhs = synthetic.ffn(shape_id, sid)
+            vp, vc, vv, _ = ops.svc(torch.from_numpy(a.row_ptr).to(dev), torch.from_numpy(a.col_idx).to(dev),
+                                    torch.from_numpy(a.values).to(dev), a.M, a.K, 16)
+            B = torch.from_numpy(rhs).to(dev)
+            C = torch.empty((vp.numel() - 1) * 16, 256, device=dev, dtype=torch.float16)
+            A = torch.randn((a.M, a.K), device=dev, dtype=torch.float16)
+
+            def t(fn, it=20):
+                for _ in range(3):
+                    fn()
+                a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a0.record()
+                for _ in range(it):
+                    fn()
+                a1.record()
+                torch.cuda.synchronize()
+                return a0.elapsed_time(a1) / it
+            ms = t(lambda: ops.sspmm(vp, vc, vv, B, 16, out=C))
+            ms_d = t(lambda: torch.matmul(A, B))
+            out.append({"shape": list(synthetic.FFN_SHAPES[shape_id]), "sparsity": synthetic.FFN_SPARSITIES[sid],
+                        "us": ms * 1e3, "useful_tflops": 2.0 * a.nnz * 256 / ms / 1e9, "cublas_dense_us": ms_d * 1e3,
+                        "cublas_useful_tflops": 2.0 * a.nnz * 256 / ms_d / 1e9, "padding": vc.numel() * 16 / a.nnz})
+    return {"note": "back-to-back launches, operands L2-resident (problem is ~1-4 MB): latency, not bandwidth",
+            "cases": out}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-extras", action="store_true", help="skip the SVC and FFN side measurements")
+    ap.add_argument("--only", default="", help="layer_id,sparsity_id,V: run a single product (profiling captures)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -168,7 +168,8 @@ int svc_begin(int M, int K, int vec_length, const int* d_csr_row_ptr, const int*
         set_error("K = %d exceeds the supported maximum of %d columns", K, kSvcMaxK);
         return (int)cudaErrorInvalidValue;
     }
-    if (!d_csr_row_ptr || (M > 0 && !d_csr_col_idx && K > 0)) { set_error("null CSR pointer"); return (int)cudaErrorInvalidValue; }
+    // d_csr_col_idx may be NULL when the matrix has no entries (it is then never read)
+    if (!d_csr_row_ptr) { set_error("null CSR row pointer"); return (int)cudaErrorInvalidValue; }
     svc_job* j = new (std::nothrow) svc_job();
     if (!j) return (int)cudaErrorMemoryAllocation;
     memset(j, 0, sizeof *j);

@@ -1,10 +1,11 @@
 """GPU parity tests of the vector-sparse SpMM, called through the C ABI, against
 the CPU oracle (fp32 restatement of the reference's host loop).
 
-Tolerance: |gpu - oracle| <= 1e-2 * max(|oracle|, eps_row) with eps_row = 1e-3 *
-the largest magnitude in that output row (outputs near zero are common with
-N(0, 0.02) weights).  fp32 output normally agrees to ~1e-5; the bound is the
-north-star's."""
+Tolerance: every element |gpu - oracle| <= 1e-2 * max(|oracle|, eps_row) with
+eps_row = 1e-3 * the largest magnitude in that output row (outputs near zero
+are common with N(0, 0.02) weights, and the tensor core sums in another order
+than the host loop), and the root-mean-square error relative to the RMS of the
+oracle <= 2e-3 for fp16 output, 1e-5 for fp32 output."""
 import numpy as np
 import pytest
 import torch
@@ -22,14 +23,18 @@ def compress(a, V):
     return (np.asarray(r.vec_row_ptr, dtype=np.int32), np.asarray(r.vec_colInd_list, dtype=np.int32), vals)
 
 
-def assert_close(got, ref, rel=1e-2):
+def assert_close(got, ref, fp32=False, rms_tol=None):
     got = np.asarray(got, dtype=np.float64)
     ref = np.asarray(ref, dtype=np.float64)
     assert got.shape == ref.shape
     assert np.isfinite(got).all()
     floor = 1e-3 * np.max(np.abs(ref), axis=1, keepdims=True) + 1e-30
     err = np.abs(got - ref) / np.maximum(np.abs(ref), floor)
-    assert err.max() <= rel, f"max rel err {err.max():.3e} at {np.unravel_index(err.argmax(), err.shape)}"
+    assert err.max() <= 1e-2, f"max rel err {err.max():.3e} at {np.unravel_index(err.argmax(), err.shape)}"
+    rms = np.sqrt(np.mean((got - ref) ** 2)) / (np.sqrt(np.mean(ref ** 2)) + 1e-30)
+    if rms_tol is None:
+        rms_tol = 1e-5 if fp32 else 2e-3
+    assert rms <= rms_tol, f"relative RMS error {rms:.3e}"
 
 
 def gpu_spmm(ptr, col, vals, rhs, V, out_dtype, row_indices=None, kernel=ops.KERNEL_AUTO):
@@ -52,7 +57,7 @@ def test_config1(lib, V, out_dtype, kernel):
     ptr, col, vals = compress(a, V)
     ref = spmm_oracle.sspmm_host(V, ptr, col, vals, rhs)
     got = gpu_spmm(ptr, col, vals, rhs, V, out_dtype, kernel=kernel)
-    assert_close(got, ref, rel=1e-2 if out_dtype == torch.float16 else 1e-3)
+    assert_close(got, ref, fp32=out_dtype == torch.float32)
 
 
 @pytest.mark.parametrize("shape_id,sparsity_id", [(0, 0), (0, 3), (0, 5), (1, 1), (1, 3), (1, 5)])
@@ -61,7 +66,7 @@ def test_ffn_v16(lib, shape_id, sparsity_id):
     ptr, col, vals = compress(a, 16)
     ref = spmm_oracle.sspmm_host(16, ptr, col, vals, rhs, threads=8)
     assert_close(gpu_spmm(ptr, col, vals, rhs, 16, torch.float16, kernel=ops.KERNEL_GATHER), ref)
-    assert_close(gpu_spmm(ptr, col, vals, rhs, 16, torch.float32, kernel=ops.KERNEL_GATHER), ref, rel=1e-3)
+    assert_close(gpu_spmm(ptr, col, vals, rhs, 16, torch.float32, kernel=ops.KERNEL_GATHER), ref, fp32=True)
 
 
 def random_cvse(rng, m_vec, K, V, lens):
@@ -82,7 +87,7 @@ def test_ragged_rows_and_column_tails(lib, V, N):
     ptr, col, vals = random_cvse(rng, len(lens), K, V, lens)
     rhs = rng.normal(0, 1, (K, N)).astype(np.float16)
     ref = spmm_oracle.sspmm_host(V, ptr, col, vals, rhs)
-    assert_close(gpu_spmm(ptr, col, vals, rhs, V, torch.float32, kernel=ops.KERNEL_GATHER), ref, rel=1e-3)
+    assert_close(gpu_spmm(ptr, col, vals, rhs, V, torch.float32, kernel=ops.KERNEL_GATHER), ref, fp32=True)
     assert_close(gpu_spmm(ptr, col, vals, rhs, V, torch.float16, kernel=ops.KERNEL_GATHER), ref)
 
 
@@ -93,7 +98,7 @@ def test_unaligned_n_uses_cuda_core_path(lib, V):
     ptr, col, vals = random_cvse(rng, len(lens), 64, V, lens)
     rhs = rng.normal(0, 1, (64, 50)).astype(np.float16)          # 50 % 8 != 0
     ref = spmm_oracle.sspmm_host(V, ptr, col, vals, rhs)
-    assert_close(gpu_spmm(ptr, col, vals, rhs, V, torch.float32), ref, rel=1e-3)
+    assert_close(gpu_spmm(ptr, col, vals, rhs, V, torch.float32), ref, fp32=True)
 
 
 def test_output_is_fully_overwritten(lib):
@@ -119,7 +124,7 @@ def test_row_swizzle_does_not_change_result(lib):
     got = gpu_spmm(ptr, col, vals, rhs, 8, torch.float32, row_indices=swz)
     assert np.array_equal(base, got)
     ref = spmm_oracle.sspmm_host(8, ptr, col, vals, rhs, threads=8)
-    assert_close(got, ref, rel=1e-3)
+    assert_close(got, ref, fp32=True)
 
 
 def test_power_law_sweep_sample(lib):
@@ -142,7 +147,7 @@ def test_conv_layer_full_width_properties(lib):
     got = gpu_spmm(ptr, col, vals, b1, V, torch.float32)
     rows = (2, 4)
     ref = spmm_oracle.sspmm_host(V, ptr, col, vals, b1, rows=rows, threads=8)
-    assert_close(got[rows[0] * V: rows[1] * V], ref, rel=1e-3)
+    assert_close(got[rows[0] * V: rows[1] * V], ref, fp32=True)
     # linearity: A(2*b1) == 2*A(b1) exactly in fp32 (power-of-two scaling)
     got2 = gpu_spmm(ptr, col, vals, (b1 * np.float16(2)).astype(np.float16), V, torch.float32)
     assert np.array_equal(got2, 2 * got)
@@ -168,5 +173,5 @@ def test_against_reference_gpu_kernel(lib, V):
     torch.cuda.synchronize()
     assert rc == 0
     ref = spmm_oracle.sspmm_host(V, ptr, col, vals, rhs)
-    assert_close(out.cpu().numpy(), ref, rel=1e-3)
-    assert_close(gpu_spmm(ptr, col, vals, rhs, V, torch.float32), out.cpu().numpy(), rel=1e-3)
+    assert_close(out.cpu().numpy(), ref, rms_tol=1e-4)
+    assert_close(gpu_spmm(ptr, col, vals, rhs, V, torch.float32), out.cpu().numpy(), rms_tol=1e-4)
