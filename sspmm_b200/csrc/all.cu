@@ -2,6 +2,7 @@
 // device symbols (status words), which needs one TU without relocatable device code.
 #include "sspmm_gather.cu"
 #include "sspmm_simt.cu"
+#include "sspmm_block.cu"
 #include "svc.cu"
 #include "c_api.cu"
 #include "cxx_api.cu"

@@ -6,6 +6,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 #include <new>
 
 #include "../../include/sspmm_b200.h"
@@ -32,6 +33,43 @@ static int fail(cudaError_t e, const char* what) {
 }
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// nvec = row_offsets[m_vec] lives in device memory; the kernel choice needs it on
+// the host.  It is read once per (pointer, m_vec, device) and remembered: weights
+// are static across calls.  A stale entry can only make the choice of kernel
+// suboptimal, never the result wrong (both kernels accept any operand).
+struct NvecEntry { const int* ptr; int m_vec; int dev; long long nvec; };
+static std::mutex g_nvec_mu;
+static NvecEntry g_nvec_cache[64];
+static int g_nvec_next = 0;
+
+static long long lookup_nvec(const int* row_offsets, int m_vec, cudaStream_t st) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    {
+        std::lock_guard<std::mutex> lk(g_nvec_mu);
+        for (const NvecEntry& e : g_nvec_cache)
+            if (e.ptr == row_offsets && e.m_vec == m_vec && e.dev == dev) return e.nvec;
+    }
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(st, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) return -1;
+    int h = 0;
+    if (cudaMemcpyAsync(&h, row_offsets + m_vec, sizeof(int), cudaMemcpyDeviceToHost, st) != cudaSuccess) return -1;
+    if (cudaStreamSynchronize(st) != cudaSuccess) return -1;
+    std::lock_guard<std::mutex> lk(g_nvec_mu);
+    g_nvec_cache[g_nvec_next] = NvecEntry{row_offsets, m_vec, dev, h};
+    g_nvec_next = (g_nvec_next + 1) % 64;
+    return h;
+}
+
+// Modelled times (seconds) of the two tensor-core kernels; constants from measurements on B200.
+static bool block_kernel_is_faster(long long nvec, const SpmmArgs& a) {
+    const double n = (double)a.N * a.batch;
+    const double mp = (double)a.m_vec * a.V;
+    const double t_gather = 2.0 * (double)nvec * n / 1.7e12 + 6e-6;
+    const double t_block = 2.0 * mp * a.K * n / 6.0e14 + 4.0 * mp * a.K / 3e12 + 12e-6;
+    return t_block < t_gather;
+}
 
 // Length-sorted scheduling order: rank by (length descending, row id ascending).
 __global__ void __launch_bounds__(256)
@@ -88,8 +126,30 @@ static int spmm_entry(int m_vec, int V, int N, int K, int batch, const int* row_
         return (int)cudaErrorInvalidValue;
     }
     cudaError_t e;
-    if (K == 0 || choice == 2 || !tc_ok) e = launch_sspmm_simt(a);
-    else e = launch_sspmm_gather(a);
+    if (K == 0 || choice == 2 || !tc_ok) {
+        e = launch_sspmm_simt(a);
+        return e == cudaSuccess ? 0 : fail(e, "SpMM launch");
+    }
+    const bool block_ok = (batch == 1 || (values_stride == 0 && K % 64 == 0)) &&
+                          sspmm_block_scratch_bytes(a) <= ((size_t)2 << 30);
+    if (choice == 3 && !block_ok) {
+        set_error("block kernel needs a shared value array (and K %% 64 == 0) for batches and <= 2 GiB of scratch");
+        return (int)cudaErrorInvalidValue;
+    }
+    bool use_block = choice == 3;
+    if (choice == 0 && block_ok) {
+        const long long nvec = lookup_nvec(row_offsets, m_vec, st);
+        use_block = nvec >= 0 && block_kernel_is_faster(nvec, a);
+    }
+    if (!use_block) {
+        e = launch_sspmm_gather(a);
+        return e == cudaSuccess ? 0 : fail(e, "SpMM launch");
+    }
+    void* scratch = nullptr;
+    e = cudaMallocAsync(&scratch, sspmm_block_scratch_bytes(a), st);
+    if (e != cudaSuccess) return fail(e, "scratch allocation for the block kernel");
+    e = launch_sspmm_block(a, scratch);
+    cudaFreeAsync(scratch, st);
     return e == cudaSuccess ? 0 : fail(e, "SpMM launch");
 }
 

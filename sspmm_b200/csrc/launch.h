@@ -28,6 +28,10 @@ struct SpmmArgs {
 
 // tcgen05 row-gather kernel.  Requires N % 8 == 0, 16-byte aligned rhs/values.
 cudaError_t launch_sspmm_gather(const SpmmArgs& a);
+// tcgen05 block kernel on a dense transposed copy of A held in `scratch`
+// (sspmm_block_scratch_bytes(a) bytes, caller-owned, stream-ordered).
+size_t sspmm_block_scratch_bytes(const SpmmArgs& a);
+cudaError_t launch_sspmm_block(const SpmmArgs& a, void* scratch);
 // CUDA-core kernel without alignment requirements.
 cudaError_t launch_sspmm_simt(const SpmmArgs& a);
 

@@ -49,7 +49,7 @@ def gpu_spmm(ptr, col, vals, rhs, V, out_dtype, row_indices=None, kernel=ops.KER
     return out.float().cpu().numpy()
 
 
-@pytest.mark.parametrize("kernel", [ops.KERNEL_GATHER, ops.KERNEL_SIMT])
+@pytest.mark.parametrize("kernel", [ops.KERNEL_GATHER, ops.KERNEL_BLOCK, ops.KERNEL_SIMT])
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.float16])
 @pytest.mark.parametrize("V", [8, 16])
 def test_config1(lib, V, out_dtype, kernel):
@@ -65,8 +65,9 @@ def test_ffn_v16(lib, shape_id, sparsity_id):
     a, rhs = synthetic.ffn(shape_id, sparsity_id)
     ptr, col, vals = compress(a, 16)
     ref = spmm_oracle.sspmm_host(16, ptr, col, vals, rhs, threads=8)
-    assert_close(gpu_spmm(ptr, col, vals, rhs, 16, torch.float16, kernel=ops.KERNEL_GATHER), ref)
-    assert_close(gpu_spmm(ptr, col, vals, rhs, 16, torch.float32, kernel=ops.KERNEL_GATHER), ref, fp32=True)
+    for kernel in (ops.KERNEL_GATHER, ops.KERNEL_BLOCK, ops.KERNEL_AUTO):
+        assert_close(gpu_spmm(ptr, col, vals, rhs, 16, torch.float16, kernel=kernel), ref)
+        assert_close(gpu_spmm(ptr, col, vals, rhs, 16, torch.float32, kernel=kernel), ref, fp32=True)
 
 
 def random_cvse(rng, m_vec, K, V, lens):
@@ -87,8 +88,9 @@ def test_ragged_rows_and_column_tails(lib, V, N):
     ptr, col, vals = random_cvse(rng, len(lens), K, V, lens)
     rhs = rng.normal(0, 1, (K, N)).astype(np.float16)
     ref = spmm_oracle.sspmm_host(V, ptr, col, vals, rhs)
-    assert_close(gpu_spmm(ptr, col, vals, rhs, V, torch.float32, kernel=ops.KERNEL_GATHER), ref, fp32=True)
-    assert_close(gpu_spmm(ptr, col, vals, rhs, V, torch.float16, kernel=ops.KERNEL_GATHER), ref)
+    for kernel in (ops.KERNEL_GATHER, ops.KERNEL_BLOCK):
+        assert_close(gpu_spmm(ptr, col, vals, rhs, V, torch.float32, kernel=kernel), ref, fp32=True)
+        assert_close(gpu_spmm(ptr, col, vals, rhs, V, torch.float16, kernel=kernel), ref)
 
 
 @pytest.mark.parametrize("V", [8, 16])
@@ -145,6 +147,9 @@ def test_conv_layer_full_width_properties(lib):
     N = synthetic.CONV_N
     b1 = rng.normal(0, 1, (a.K, N)).astype(np.float16)
     got = gpu_spmm(ptr, col, vals, b1, V, torch.float32)
+    got_gather = gpu_spmm(ptr, col, vals, b1, V, torch.float32, kernel=ops.KERNEL_GATHER)
+    got_block = gpu_spmm(ptr, col, vals, b1, V, torch.float32, kernel=ops.KERNEL_BLOCK)
+    assert_close(got_block, got_gather, fp32=True)
     rows = (2, 4)
     ref = spmm_oracle.sspmm_host(V, ptr, col, vals, b1, rows=rows, threads=8)
     assert_close(got[rows[0] * V: rows[1] * V], ref, fp32=True)
