@@ -230,23 +230,46 @@ def run_ours(args):
     barrier()
     assert ops.device_status() == 0
 
+    # The 32 launches of a step are replayed from one CUDA graph (what a deployment
+    # of a fixed layer stack does); falls back to eager launches if capture fails.
+    run_step, graphed = step, False
+    if not args.no_graph:
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                step()
+            graph.replay()
+            torch.cuda.synchronize()
+            run_step, graphed = graph.replay, True
+        except Exception as exc:  # pragma: no cover - depends on driver support
+            sys.stderr.write(f"CUDA graph capture failed, timing eager launches: {exc}\n")
+            torch.cuda.synchronize()
+
     # ---- timed region: K steps, per-step and per-launch CUDA events on the launching stream
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
         time.sleep(0.3)
     step_evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
-    launch_evs = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in probs]
-                  for _ in range(args.steps)]
     barrier()
     wall0 = time.perf_counter()
     for k in range(args.steps):
         flush.zero_()                       # evicts L2 between steps (outside the step's events)
         step_evs[k][0].record()
-        step(launch_evs[k])
+        run_step()
         step_evs[k][1].record()
     barrier()
     wall = time.perf_counter() - wall0
+    # second, eager pass with an event pair around every launch: per-kernel durations for the roofline
+    prof_steps = min(args.steps, 5)
+    launch_evs = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in probs]
+                  for _ in range(prof_steps)]
+    step()                                  # one untimed eager step after the graph replays
+    barrier()
+    for k in range(prof_steps):
+        flush.zero_()
+        step(launch_evs[k])
+    barrier()
     clocks = sampler.stop() if rank == 0 else None
     step_ms = [a.elapsed_time(b) for a, b in step_evs]
     total_ms = float(sum(step_ms))
@@ -371,7 +394,7 @@ def run_ours(args):
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
                 "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
                 "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-                "config": {"workload": WORKLOAD if not args.only else "single product " + args.only, "N_total": N_total, "N_per_gpu": n_loc, "products_per_step": len(probs),
+                "config": {"workload": WORKLOAD if not args.only else "single product " + args.only, "N_total": N_total, "N_per_gpu": n_loc, "products_per_step": len(probs), "cuda_graph": graphed,
                            "l2": "operands of a step exceed L2 and a 256 MiB buffer is written between steps",
                            "parallelism": f"B and C column-sharded over {world} GPU(s), A_vs replicated, no collective"},
                 "roofline": roof, "cpu_baseline": cpu, "e2e": e2e,
@@ -458,6 +481,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of a CUDA graph of the step")
     ap.add_argument("--no-extras", action="store_true", help="skip the SVC and FFN side measurements")
     ap.add_argument("--only", default="", help="layer_id,sparsity_id,V: run a single product (profiling captures)")
     args = ap.parse_args()

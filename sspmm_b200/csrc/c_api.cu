@@ -130,10 +130,12 @@ static int spmm_entry(int m_vec, int V, int N, int K, int batch, const int* row_
         e = launch_sspmm_simt(a);
         return e == cudaSuccess ? 0 : fail(e, "SpMM launch");
     }
-    const bool block_ok = (batch == 1 || (values_stride == 0 && K % 64 == 0)) &&
+    const int64_t oes = out_f16 ? 2 : 4;
+    const bool block_ok = (batch == 1 || (values_stride == 0 && (rhs_stride * 2) % 16 == 0 && (out_stride * oes) % 16 == 0)) &&
+                          aligned16(out) && ((int64_t)N * oes) % 16 == 0 &&
                           sspmm_block_scratch_bytes(a) <= ((size_t)2 << 30);
     if (choice == 3 && !block_ok) {
-        set_error("block kernel needs a shared value array (and K %% 64 == 0) for batches and <= 2 GiB of scratch");
+        set_error("block kernel needs 16-byte aligned output, a shared value array for batches and <= 2 GiB of scratch");
         return (int)cudaErrorInvalidValue;
     }
     bool use_block = choice == 3;

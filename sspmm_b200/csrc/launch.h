@@ -4,6 +4,8 @@
 #include <cuda_fp16.h>
 #include <stdint.h>
 
+#include <atomic>
+
 namespace sspmm_b200 {
 
 struct SpmmArgs {
@@ -34,6 +36,27 @@ size_t sspmm_block_scratch_bytes(const SpmmArgs& a);
 cudaError_t launch_sspmm_block(const SpmmArgs& a, void* scratch);
 // CUDA-core kernel without alignment requirements.
 cudaError_t launch_sspmm_simt(const SpmmArgs& a);
+
+// Per-device "already done" flags for one-time, per-device set-up (function
+// attributes are per device).  Supports device ordinals 0..63.
+class DeviceOnce {
+public:
+    bool done() const {
+        int d = 0;
+        cudaGetDevice(&d);
+        return d >= 0 && d < 64 && (mask_.load(std::memory_order_acquire) >> d) & 1ull;
+    }
+    void mark() {
+        int d = 0;
+        cudaGetDevice(&d);
+        if (d >= 0 && d < 64) mask_.fetch_or(1ull << d, std::memory_order_release);
+    }
+private:
+    std::atomic<unsigned long long> mask_{0};
+};
+
+// Multiprocessor count of the current device (cached per device ordinal).
+int current_device_sm_count();
 
 // Records a message retrievable through sspmm_last_error_string().
 void set_error(const char* fmt, ...);

@@ -16,7 +16,8 @@
 //   MMA B       B  tile [64 k][BN n],  N-major, 128-byte swizzle  (TMA 2-D boxes 64 x 64)
 //   D           TMEM, lane = row of C, column = column of C, two accumulators
 //   warps       0 TMA producer, 1 MMA issuer / TMEM owner, 4-7 epilogue
-//   epilogue    tcgen05.ld 32 columns at a time -> fp16/fp32 -> 16-byte stores
+//   epilogue    tcgen05.ld 32 columns at a time -> fp16/fp32 -> 64-byte rows in a swizzled
+//               staging tile -> TMA store (clips the M and N tails, keeps stores off the LSU)
 #include <cuda.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -32,24 +33,43 @@ constexpr int kBK = 64;
 constexpr int kBlockThreads = 256;
 
 // ---- expansion of the compressed operand ------------------------------------
-// blockIdx.y = vector row, blockIdx.x strides over its vectors; each thread
-// writes the V values of one vector as one or two 16-byte stores into row
-// column_indices[j] of At.
+// At[k][i*V .. i*V+V) = values of the vector of row i at column k, or zeros.
+// One CTA per (vector row i, chunk of kExpandChunk columns): the row's column
+// list is turned into a column -> vector map in shared memory, then every
+// column of the chunk is written (value vector or zeros), so no separate zero
+// fill of At is needed.
+constexpr int kExpandChunk = 1024;
+
 template <int V>
 __global__ void __launch_bounds__(256)
 expand_transposed_kernel(int m_vec, int K, const int* __restrict__ row_offsets, const int* __restrict__ col,
                          const __half* __restrict__ values, __half* __restrict__ at) {
+    __shared__ int slot[kExpandChunk];
     const int64_t mp = (int64_t)m_vec * V;
+    const int k_begin = blockIdx.x * kExpandChunk;
+    const int k_end = min(K, k_begin + kExpandChunk);
     for (int i = blockIdx.y; i < m_vec; i += gridDim.y) {
+        for (int k = threadIdx.x; k < kExpandChunk; k += blockDim.x) slot[k] = -1;
+        __syncthreads();
         const int j0 = row_offsets[i], j1 = row_offsets[i + 1];
-        for (int j = j0 + blockIdx.x * blockDim.x + threadIdx.x; j < j1; j += gridDim.x * blockDim.x) {
-            const unsigned c = (unsigned)col[j];
-            if (c >= (unsigned)K) continue;
-            const uint4* src = reinterpret_cast<const uint4*>(values + (int64_t)j * V);
-            uint4* dst = reinterpret_cast<uint4*>(at + (int64_t)c * mp + (int64_t)i * V);
-#pragma unroll
-            for (int q = 0; q < V / 8; ++q) dst[q] = __ldg(src + q);
+        for (int j = j0 + threadIdx.x; j < j1; j += blockDim.x) {
+            const int c = col[j];
+            if (c >= k_begin && c < k_end) slot[c - k_begin] = j;      // duplicates: one of them wins
         }
+        __syncthreads();
+        for (int k = k_begin + threadIdx.x; k < k_end; k += blockDim.x) {
+            const int j = slot[k - k_begin];
+            uint4* dst = reinterpret_cast<uint4*>(at + (int64_t)k * mp + (int64_t)i * V);
+            if (j >= 0) {
+                const uint4* src = reinterpret_cast<const uint4*>(values + (int64_t)j * V);
+#pragma unroll
+                for (int q = 0; q < V / 8; ++q) dst[q] = __ldg(src + q);
+            } else {
+#pragma unroll
+                for (int q = 0; q < V / 8; ++q) dst[q] = make_uint4(0, 0, 0, 0);
+            }
+        }
+        __syncthreads();
     }
 }
 
@@ -60,7 +80,9 @@ struct BlockLayout {
     static constexpr int kChunk = kBK * 128;                     // 8 KB
     static constexpr int kAOff = 0;
     static constexpr int kBOff = STAGES * kAStage;
-    static constexpr int kBarOff = kBOff + STAGES * kBStage;
+    static constexpr int kOutBuf = kBM * 64;                     // 128 rows x 64 bytes
+    static constexpr int kOutOff = kBOff + STAGES * kBStage;     // two staging buffers for the TMA store
+    static constexpr int kBarOff = kOutOff + 2 * kOutBuf;
     static constexpr int kNumBars = 2 * STAGES + 4;
     static constexpr int kTmemPtrOff = kBarOff + kNumBars * 8;
     static constexpr int kAbortOff = kTmemPtrOff + 8;
@@ -78,7 +100,7 @@ struct BlockProblem {
 template <int BN, int STAGES, typename OutT>
 __global__ void __launch_bounds__(kBlockThreads, 1)
 sspmm_block_kernel(const __grid_constant__ CUtensorMap tmap_at, const __grid_constant__ CUtensorMap tmap_b,
-                   BlockProblem p, OutT* __restrict__ out) {
+                   const __grid_constant__ CUtensorMap tmap_c, BlockProblem p) {
     using L = BlockLayout<BN, STAGES>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -104,6 +126,7 @@ sspmm_block_kernel(const __grid_constant__ CUtensorMap tmap_at, const __grid_con
         mbar_fence_init();
         tma_prefetch_desc(&tmap_at);
         tma_prefetch_desc(&tmap_b);
+        tma_prefetch_desc(&tmap_c);
     }
     if (warp == 1) {
         tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_ptr_smem)), L::kTmemCols);
@@ -133,7 +156,7 @@ sspmm_block_kernel(const __grid_constant__ CUtensorMap tmap_at, const __grid_con
                     for (int c = 0; c < kBM / 64; ++c) tma_load_2d(a_s + c * L::kChunk, &tmap_at, m0 + 64 * c, ks * kBK, full);
 #pragma unroll
                     for (int c = 0; c < BN / 64; ++c)
-                        tma_load_2d(b_s + c * L::kChunk, &tmap_b, n0 + 64 * c, b * p.K + ks * kBK, full);
+                        tma_load_3d(b_s + c * L::kChunk, &tmap_b, n0 + 64 * c, ks * kBK, b, full);
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
                 if (!ok) break;
@@ -173,63 +196,75 @@ sspmm_block_kernel(const __grid_constant__ CUtensorMap tmap_at, const __grid_con
             ++acc_it;
         }
     } else if (warp >= 4) {
+        // Each thread owns one row of the 128-row tile.  Per 32 accumulator columns: TMEM -> registers ->
+        // 64-byte row pieces in a staging tile (64-byte swizzle, conflict-free) -> one TMA store.
+        constexpr int kColsPerStore = 64 / (int)sizeof(OutT);          // 32 (fp16) or 16 (fp32)
+        constexpr int kStoresPerLoad = 32 / kColsPerStore;
         const int q = warp & 3;
-        uint32_t acc_it = 0;
-        for (int T = blockIdx.x; T < p.total_tiles; T += gridDim.x) {
+        const int row = q * 32 + lane;
+        const bool issuer = (threadIdx.x == 128);
+        const uint32_t swz = (uint32_t)((row >> 1) & 3);
+        uint32_t acc_it = 0, st_it = 0;
+        bool ok = true;
+        for (int T = blockIdx.x; ok && T < p.total_tiles; T += gridDim.x) {
             const int b = T / tiles_per_batch, r = T % tiles_per_batch;
             const int m0 = (r % p.m_tiles) * kBM, n0 = (r / p.m_tiles) * BN;
             const uint32_t buf = acc_it & 1u, acc_phase = (acc_it >> 1) & 1u;
-            const int m = m0 + q * 32 + lane;
-            OutT* orow = out + (int64_t)b * p.out_stride + (int64_t)m * p.N;
-            if (k_steps > 0) {
-                if (!mbar_wait(bar_acc_full + 8 * buf, acc_phase, abort_flag, kStatusWaitBlock)) break;
-                tc_fence_after_sync();
-            }
+            // the four warps must agree on leaving: they meet at named barriers below
+            if (!named_barrier_and(2, 128, mbar_wait(bar_acc_full + 8 * buf, acc_phase, abort_flag, kStatusWaitBlock))) break;
+            tc_fence_after_sync();
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN;
-#pragma unroll 1
-            for (int cc = 0; cc < BN / 32; ++cc) {
-                uint32_t v[32];
-                if (k_steps > 0) {
-                    tmem_ld_x32(taddr + cc * 32, v);
-                    tc_wait_ld();
-                } else {
+            uint32_t v[2][32];
+            tmem_ld_x32(taddr, v[0]);
 #pragma unroll
-                    for (int e = 0; e < 32; ++e) v[e] = 0u;
-                }
-                if (cc == BN / 32 - 1 && k_steps > 0) {
+            for (int cc = 0; cc < BN / 32; ++cc) {
+                tc_wait_ld();
+                if (cc + 1 < BN / 32) {
+                    tmem_ld_x32(taddr + (cc + 1) * 32, v[(cc + 1) & 1]);       // in flight while this chunk is stored
+                } else {
                     tc_fence_before_sync();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(bar_acc_empty + 8 * buf);
+                    if (lane == 0) mbar_arrive(bar_acc_empty + 8 * buf);        // accumulator drained
                 }
-                const int n = n0 + cc * 32;
-                if (m < p.Mp) {
+                const uint32_t(&w)[32] = v[cc & 1];
+#pragma unroll
+                for (int h = 0; h < kStoresPerLoad; ++h) {
+                    const uint32_t sb = st_it & 1u;
+                    uint8_t* stage_row = smem + L::kOutOff + sb * L::kOutBuf + row * 64;
+                    named_barrier_sync(1, 128);          // the issuer has seen the store that last read this buffer finish
                     if constexpr (sizeof(OutT) == 2) {
 #pragma unroll
                         for (int g = 0; g < 4; ++g) {
-                            if (n + g * 8 + 8 <= p.N) {
-                                uint4 w;
-                                __half2 h0 = __floats2half2_rn(__uint_as_float(v[g * 8 + 0]), __uint_as_float(v[g * 8 + 1]));
-                                __half2 h1 = __floats2half2_rn(__uint_as_float(v[g * 8 + 2]), __uint_as_float(v[g * 8 + 3]));
-                                __half2 h2 = __floats2half2_rn(__uint_as_float(v[g * 8 + 4]), __uint_as_float(v[g * 8 + 5]));
-                                __half2 h3 = __floats2half2_rn(__uint_as_float(v[g * 8 + 6]), __uint_as_float(v[g * 8 + 7]));
-                                w.x = *reinterpret_cast<uint32_t*>(&h0); w.y = *reinterpret_cast<uint32_t*>(&h1);
-                                w.z = *reinterpret_cast<uint32_t*>(&h2); w.w = *reinterpret_cast<uint32_t*>(&h3);
-                                *reinterpret_cast<uint4*>(orow + n + g * 8) = w;
-                            }
+                            uint4 o;
+                            __half2 h0 = __floats2half2_rn(__uint_as_float(w[g * 8 + 0]), __uint_as_float(w[g * 8 + 1]));
+                            __half2 h1 = __floats2half2_rn(__uint_as_float(w[g * 8 + 2]), __uint_as_float(w[g * 8 + 3]));
+                            __half2 h2 = __floats2half2_rn(__uint_as_float(w[g * 8 + 4]), __uint_as_float(w[g * 8 + 5]));
+                            __half2 h3 = __floats2half2_rn(__uint_as_float(w[g * 8 + 6]), __uint_as_float(w[g * 8 + 7]));
+                            o.x = *reinterpret_cast<uint32_t*>(&h0); o.y = *reinterpret_cast<uint32_t*>(&h1);
+                            o.z = *reinterpret_cast<uint32_t*>(&h2); o.w = *reinterpret_cast<uint32_t*>(&h3);
+                            *reinterpret_cast<uint4*>(stage_row + (((uint32_t)g ^ swz) << 4)) = o;
                         }
                     } else {
 #pragma unroll
-                        for (int g = 0; g < 8; ++g) {
-                            if (n + g * 4 + 4 <= p.N) {
-                                uint4 w = make_uint4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
-                                *reinterpret_cast<uint4*>(orow + n + g * 4) = w;
-                            }
+                        for (int g = 0; g < 4; ++g) {
+                            const int e = h * 16 + g * 4;
+                            *reinterpret_cast<uint4*>(stage_row + (((uint32_t)g ^ swz) << 4)) =
+                                make_uint4(w[e], w[e + 1], w[e + 2], w[e + 3]);
                         }
                     }
+                    fence_proxy_async_smem();
+                    named_barrier_sync(1, 128);          // the staging tile is complete
+                    if (issuer) {
+                        tma_store_3d(&tmap_c, sbase + L::kOutOff + sb * L::kOutBuf, n0 + cc * 32 + h * kColsPerStore, m0, b);
+                        tma_store_commit();
+                        tma_store_wait_read<1>();        // the other buffer's store has finished reading
+                    }
+                    ++st_it;
                 }
             }
             ++acc_it;
         }
+        if (issuer) tma_store_wait_all<0>();
     }
     tc_fence_before_sync();
     __syncthreads();
@@ -244,12 +279,15 @@ using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, voi
                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 EncodeFn block_encode_fn() {
-    void* fn = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess ||
-        q != cudaDriverEntryPointSuccess)
-        return nullptr;
-    return reinterpret_cast<EncodeFn>(fn);
+    static EncodeFn cached = [] {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            fn = nullptr;
+        return reinterpret_cast<EncodeFn>(fn);
+    }();
+    return cached;
 }
 
 bool encode_2d(EncodeFn enc, CUtensorMap* m, const void* base, uint64_t inner, uint64_t outer, uint32_t box_inner,
@@ -263,14 +301,31 @@ bool encode_2d(EncodeFn enc, CUtensorMap* m, const void* base, uint64_t inner, u
                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// 3-D map {inner, rows, batch} with a 64 x `box_rows` x 1 box (in elements: box_inner x box_rows x 1).
+bool encode_3d(EncodeFn enc, CUtensorMap* m, CUtensorMapDataType dt, size_t es, const void* base, uint64_t inner,
+               uint64_t rows, uint64_t batch, uint64_t batch_stride_elems, uint32_t box_inner, uint32_t box_rows,
+               CUtensorMapSwizzle swz) {
+    const cuuint64_t gdim[3] = {inner, rows, batch};
+    const cuuint64_t gstride[2] = {inner * es, (batch > 1 ? batch_stride_elems : inner * rows) * es};
+    const cuuint32_t box[3] = {box_inner, box_rows, 1u};
+    const cuuint32_t estr[3] = {1u, 1u, 1u};
+    return enc(m, dt, 3, const_cast<void*>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
+               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <int BN, int STAGES, typename OutT>
-cudaError_t launch_block(const SpmmArgs& a, const CUtensorMap& ta, const CUtensorMap& tb, const BlockProblem& p, int sms) {
+cudaError_t launch_block(const SpmmArgs& a, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
+                         const BlockProblem& p, int sms) {
     using L = BlockLayout<BN, STAGES>;
     auto kern = sspmm_block_kernel<BN, STAGES, OutT>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
-    if (e != cudaSuccess) return e;
+    static DeviceOnce attr_once;                      // one flag set per instantiation
+    if (!attr_once.done()) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
+        if (e != cudaSuccess) return e;
+        attr_once.mark();
+    }
     const int grid = p.total_tiles < sms ? p.total_tiles : sms;
-    kern<<<grid, kBlockThreads, L::kDynamic, a.stream>>>(ta, tb, p, static_cast<OutT*>(a.out));
+    kern<<<grid, kBlockThreads, L::kDynamic, a.stream>>>(ta, tb, tc, p);
     return cudaGetLastError();
 }
 
@@ -293,14 +348,10 @@ cudaError_t launch_sspmm_block(const SpmmArgs& a, void* scratch) {
     }
     const int Mp = a.m_vec * a.V;
     __half* at = static_cast<__half*>(scratch);
-    cudaError_t e = cudaMemsetAsync(at, 0, sspmm_block_scratch_bytes(a), a.stream);
-    if (e != cudaSuccess) return e;
+    cudaError_t e;
     {
-        // enough blocks per vector row to cover up to K vectors, a few thousand blocks at most
-        int bx = (a.K + 255) / 256;
-        if (bx > 32) bx = 32;
         const int by = a.m_vec < 32768 ? a.m_vec : 32768;
-        const dim3 grid(bx, by);
+        const dim3 grid((a.K + kExpandChunk - 1) / kExpandChunk, by);
         if (a.V == 16)
             expand_transposed_kernel<16><<<grid, 256, 0, a.stream>>>(a.m_vec, a.K, a.row_offsets, a.column_indices, a.values, at);
         else
@@ -308,9 +359,7 @@ cudaError_t launch_sspmm_block(const SpmmArgs& a, void* scratch) {
         e = cudaGetLastError();
         if (e != cudaSuccess) return e;
     }
-    int dev = 0, sms = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int sms = current_device_sm_count();
     if (sms <= 0) return cudaErrorNoDevice;
 
     const int m_tiles = (Mp + kBM - 1) / kBM;
@@ -321,21 +370,26 @@ cudaError_t launch_sspmm_block(const SpmmArgs& a, void* scratch) {
     p.Mp = Mp; p.N = a.N; p.K = a.K;
     p.m_tiles = m_tiles; p.n_tiles = (a.N + BN - 1) / BN;
     const int64_t total = (int64_t)p.m_tiles * p.n_tiles * a.batch;
-    if (total > 0x7fffffffLL || (int64_t)a.K * a.batch > 0x7fffffffLL) {
+    if (total > 0x7fffffffLL) {
         set_error("problem too large for 32-bit tile ids");
         return cudaErrorInvalidValue;
     }
     p.total_tiles = (int)total;
     p.out_stride = a.out_stride;
-    CUtensorMap ta, tb;
+    CUtensorMap ta, tb, tc;
+    const size_t oes = a.out_f16 ? 2 : 4;
     if (!encode_2d(enc, &ta, at, (uint64_t)Mp, (uint64_t)a.K, 64, 64) ||
-        !encode_2d(enc, &tb, a.rhs, (uint64_t)a.N, (uint64_t)a.K * a.batch, 64, 64)) {
-        set_error("cuTensorMapEncodeTiled failed (Mp=%d N=%d K=%d)", Mp, a.N, a.K);
+        !encode_3d(enc, &tb, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a.rhs, (uint64_t)a.N, (uint64_t)a.K, (uint64_t)a.batch,
+                   (uint64_t)a.rhs_stride, 64, 64, CU_TENSOR_MAP_SWIZZLE_128B) ||
+        !encode_3d(enc, &tc, a.out_f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, oes, a.out,
+                   (uint64_t)a.N, (uint64_t)Mp, (uint64_t)a.batch, (uint64_t)a.out_stride, (uint32_t)(64 / oes), 128,
+                   CU_TENSOR_MAP_SWIZZLE_64B)) {
+        set_error("cuTensorMapEncodeTiled failed (Mp=%d N=%d K=%d batch=%d)", Mp, a.N, a.K, a.batch);
         return cudaErrorInvalidValue;
     }
     if (wide)
-        return a.out_f16 ? launch_block<256, 4, __half>(a, ta, tb, p, sms) : launch_block<256, 4, float>(a, ta, tb, p, sms);
-    return a.out_f16 ? launch_block<128, 6, __half>(a, ta, tb, p, sms) : launch_block<128, 6, float>(a, ta, tb, p, sms);
+        return a.out_f16 ? launch_block<256, 4, __half>(a, ta, tb, tc, p, sms) : launch_block<256, 4, float>(a, ta, tb, tc, p, sms);
+    return a.out_f16 ? launch_block<128, 6, __half>(a, ta, tb, tc, p, sms) : launch_block<128, 6, float>(a, ta, tb, tc, p, sms);
 }
 
 }  // namespace sspmm_b200

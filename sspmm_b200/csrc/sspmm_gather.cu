@@ -344,25 +344,34 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
-int sm_count() {
-    int dev = 0, n = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
-    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
-    return n;
-}
 
 template <int V, typename OutT, int KS, int STAGES>
 cudaError_t launch_one(const SpmmArgs& a, const CUtensorMap& tmap, const Problem& p, int grid) {
     using L = Layout<KS, STAGES>;
     auto kern = sspmm_gather_kernel<V, OutT, KS, STAGES>;
-    // per call: the attribute belongs to the current device's copy of the function
-    cudaError_t attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
-    if (attr_err != cudaSuccess) return attr_err;
+    static DeviceOnce attr_once;                      // one flag set per instantiation
+    if (!attr_once.done()) {
+        cudaError_t attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
+        if (attr_err != cudaSuccess) return attr_err;
+        attr_once.mark();
+    }
     kern<<<grid, kThreads, L::kDynamic, a.stream>>>(tmap, p, static_cast<OutT*>(a.out));
     return cudaGetLastError();
 }
 
 }  // namespace
+
+int current_device_sm_count() {
+    static std::atomic<int> cache[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+    int n = cache[dev].load(std::memory_order_relaxed);
+    if (n == 0) {
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+        cache[dev].store(n, std::memory_order_relaxed);
+    }
+    return n;
+}
 
 cudaError_t launch_sspmm_gather(const SpmmArgs& a) {
     EncodeTiledFn enc = encode_fn();
@@ -392,7 +401,7 @@ cudaError_t launch_sspmm_gather(const SpmmArgs& a) {
     p.m_vec = a.m_vec; p.N = a.N; p.K = a.K; p.n_tiles = n_tiles; p.total_tiles = (int)total;
     p.row_indices = a.row_indices; p.row_offsets = a.row_offsets; p.col = a.column_indices; p.values = a.values;
     p.values_stride = a.values_stride; p.out_stride = a.out_stride;
-    const int sms = sm_count();
+    const int sms = current_device_sm_count();
     if (sms <= 0) return cudaErrorNoDevice;
     const int grid = (int)(total < sms ? total : sms);
 

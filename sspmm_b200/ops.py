@@ -54,9 +54,15 @@ def sspmm(row_offsets: torch.Tensor, column_indices: torch.Tensor, values: torch
     if out is None:
         out = torch.empty((m_vec * vec_length, N), dtype=out_dtype, device=rhs.device)
     fn = capi.lib().sspmm_f16_f16 if out.dtype == torch.float16 else capi.lib().sspmm_f16_f32
-    with torch.cuda.device(rhs.device):
-        capi.check(fn(m_vec, vec_length, N, K, _ptr(row_indices), row_offsets.data_ptr(), column_indices.data_ptr(),
-                      values.data_ptr(), rhs.data_ptr(), out.data_ptr(), _stream_ptr()))
+    args = (m_vec, vec_length, N, K, _ptr(row_indices), row_offsets.data_ptr(), column_indices.data_ptr(),
+            values.data_ptr(), rhs.data_ptr(), out.data_ptr())
+    if torch.cuda.current_device() == rhs.device.index:
+        rc = fn(*args, _stream_ptr())
+    else:
+        with torch.cuda.device(rhs.device):
+            rc = fn(*args, _stream_ptr())
+    if rc != 0:
+        capi.check(rc)
     return out
 
 
