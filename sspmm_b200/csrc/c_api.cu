@@ -32,6 +32,21 @@ static int fail(cudaError_t e, const char* what) {
     return (int)e;
 }
 
+// The stream-ordered allocator returns memory to the OS at every synchronisation unless told to
+// keep some; scratch is requested per call, so let the pool keep up to 1 GiB (once per device).
+static void keep_pool_memory() {
+    static DeviceOnce once;
+    if (once.done()) return;
+    int dev = 0;
+    cudaMemPool_t pool;
+    if (cudaGetDevice(&dev) == cudaSuccess && cudaDeviceGetDefaultMemPool(&pool, dev) == cudaSuccess) {
+        unsigned long long cur = 0, want = 1ull << 30;
+        if (cudaMemPoolGetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &cur) == cudaSuccess && cur < want)
+            cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &want);
+    }
+    once.mark();
+}
+
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // nvec = row_offsets[m_vec] lives in device memory; the kernel choice needs it on
@@ -148,6 +163,7 @@ static int spmm_entry(int m_vec, int V, int N, int K, int batch, const int* row_
         return e == cudaSuccess ? 0 : fail(e, "SpMM launch");
     }
     void* scratch = nullptr;
+    keep_pool_memory();
     e = cudaMallocAsync(&scratch, sspmm_block_scratch_bytes(a), st);
     if (e != cudaSuccess) return fail(e, "scratch allocation for the block kernel");
     e = launch_sspmm_block(a, scratch);
@@ -165,6 +181,7 @@ struct svc_job {
     bool with_values;
     long long nvec;
     long long table_ints;
+    long long class_groups[6];
     int device;
     cudaStream_t stream;
 };
@@ -246,8 +263,9 @@ int svc_begin(int M, int K, int vec_length, const int* d_csr_row_ptr, const int*
     // one allocation: vec_ptr[mv+1] | mode[mv] | tbl_len[mv] | pad | tbl_off[mv+1] | totals[2]
     const size_t ints = (mv + 1) + mv + mv;
     const size_t ints_padded = (ints + 3) & ~(size_t)3;
-    const size_t bytes = ints_padded * 4 + (mv + 1 + 2) * 8;
+    const size_t bytes = ints_padded * 4 + (mv + 1 + kSvcTotals) * 8;
     void* base = nullptr;
+    keep_pool_memory();
     cudaError_t e = cudaMallocAsync(&base, bytes, st);
     if (e != cudaSuccess) { delete j; return fail(e, "scratch allocation"); }
     j->s.vec_ptr = static_cast<int*>(base);
@@ -257,7 +275,7 @@ int svc_begin(int M, int K, int vec_length, const int* d_csr_row_ptr, const int*
     j->s.totals = j->s.tbl_off + mv + 1;
     j->s.tables = nullptr;
     e = svc_count_and_scan(j->p, j->s, j->with_values, st);
-    long long totals[2] = {0, 0};
+    long long totals[kSvcTotals] = {0};
     if (e == cudaSuccess) e = cudaMemcpyAsync(totals, j->s.totals, sizeof totals, cudaMemcpyDeviceToHost, st);
     if (e == cudaSuccess) e = cudaStreamSynchronize(st);
     int bad = 0;
@@ -272,6 +290,7 @@ int svc_begin(int M, int K, int vec_length, const int* d_csr_row_ptr, const int*
     }
     j->nvec = totals[0];
     j->table_ints = totals[1];
+    for (int c = 0; c < 6; ++c) j->class_groups[c] = totals[2 + c];
     *nvec = totals[0];
     *job = j;
     return 0;
@@ -293,7 +312,7 @@ int svc_finish(svc_job* j, int* d_vec_row_ptr, int* d_vec_col, void* d_vec_value
         e = cudaMallocAsync(reinterpret_cast<void**>(&j->s.tables), (size_t)j->table_ints * 4, st);
         if (e != cudaSuccess) return fail(e, "table scratch allocation");
     }
-    e = svc_emit(j->p, j->s, d_vec_col, ov, st);
+    e = svc_emit(j->p, j->s, j->class_groups, d_vec_col, ov, st);
     if (e != cudaSuccess) return fail(e, "SVC emit");
     j->stream = st;
     return 0;

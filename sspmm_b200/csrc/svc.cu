@@ -5,25 +5,34 @@
 //     for j in 0..V-1 (rows below M only):  cols = list(set(cols + row[V*i+j]))
 // and the vector row pointer is the running sum of len(cols).  The order of `cols`
 // is CPython's set order, which for small non-negative ints is decided by an
-// open-addressing table (hash(x) = x; probe nine neighbours when the window fits,
-// else jump to (5*i + 1 + perturb) & mask; the table grows to the power of two
-// above 4*used -- 2*used beyond 50 000 -- once 5*fill >= 3*mask, re-inserting in
-// slot order; iteration is in slot order).
+// open-addressing table: hash(x) = x; start slot x & mask; probe the nine following
+// slots when that window fits inside the table, else jump to (5*i + 1 + perturb) & mask
+// with perturb >>= 5; after an insertion with 5*fill >= 3*mask the table is rebuilt
+// with the power-of-two length above 4*used (2*used beyond 50 000), re-inserting
+// the old entries in slot order; iteration is in slot order.
 //
-// Kernels, one warp per vector row (the V rows of a group are one contiguous
-// CSR range):
+// A "team" (one warp, or one CTA) works on one vector row; the V rows of a group
+// are one contiguous CSR range.
 //   svc_count_kernel   marks the group's columns in a shared-memory bitmap with
-//                      atomicOr, counts first-time bits by ballot-free popc of
-//                      the returned words, and decides per group whether
-//                      ascending order is already the exact answer: it is when
-//                      the largest column id is below the final table length,
-//                      because then every key sits in its home slot.
-//   svc_scan_kernel    exclusive scans (vector row pointers, scratch offsets).
-//   svc_emit_sorted    rebuilds the bitmap, turns it into the ascending column
-//                      list with a popc prefix scan across the warp, and places
-//                      value vectors with prefix[word] + popc(lower bits).
-//   svc_emit_replay    replays the V set rebuilds in a scratch table, exactly.
+//                      atomicOr, counts first-time bits by popc of the returned
+//                      words, and decides per group whether ascending order is
+//                      already the exact answer: it is when the largest column id
+//                      is below the final table length (every key then sits in its
+//                      home slot).
+//   svc_scan_kernel    exclusive scans (vector row pointers, scratch offsets) and a
+//                      histogram of replay classes.
+//   svc_emit_sorted    bitmap -> ascending column list by a popc prefix scan; value
+//                      vectors placed with prefix[word] + popc(lower bits).
+//   svc_emit_replay    exact replay of the V set rebuilds.  Insertion into a table of
+//                      fixed length is "first come, first served" along each key's
+//                      probe path, which has a unique fixed point: slot = the first
+//                      one on my path not held by an earlier element.  The team finds
+//                      it in parallel with atomicMin on the element's sequence number;
+//                      table growth steps are replayed level by level (8, 32, 128, ...).
 #include "svc.cuh"
+
+#include <cstdio>
+#include <mutex>
 
 #include "launch.h"
 
@@ -31,31 +40,75 @@ namespace sspmm_b200 {
 
 __device__ int g_svc_bad_column = 0;
 
+#ifdef SVC_PROFILE
+__device__ unsigned long long g_svc_prof[8 * 8];     // [class][phase] cycles of thread 0 of each team
+#define PROF_DECL long long prof_t = clock64(); long long prof_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#define PROF_MARK(ph) { const long long now_ = clock64(); prof_acc[ph] += now_ - prof_t; prof_t = now_; }
+#define PROF_FLUSH(cls) if (Team::tid() == 0) { for (int k_ = 0; k_ < 8; ++k_) atomicAdd(&g_svc_prof[(cls) * 8 + k_], (unsigned long long)prof_acc[k_]); atomicAdd(&g_svc_prof[(cls) * 8 + 7], 1ull); }
+#else
+#define PROF_DECL
+#define PROF_MARK(ph)
+#define PROF_FLUSH(cls)
+#endif
+
 namespace {
 
 constexpr int kMinTable = 8;
 constexpr int kLinearProbes = 9;
 constexpr int kPerturbShift = 5;
+constexpr int kEmptyPrio = 0x7fffffff;
+
+// Replay classes by number of distinct columns u (and final table length):
+constexpr int kClassSorted = 0;   // no replay
+constexpr int kClassS = 1;        // u <= 306   (table <= 512):   warp team, everything in shared memory
+constexpr int kClassM1 = 2;       // u <= 1228  (table <= 2048):  CTA team, everything in shared memory
+constexpr int kClassM2 = 3;       // u <= 4914  (table <= 8192):  CTA team, everything in shared memory
+constexpr int kClassL = 4;        // table <= 32768:              CTA team, table in shared memory, lists in global
+constexpr int kClassXL = 5;       // larger:                      CTA team, table and lists in global
+constexpr int kNumClasses = 6;
+
+constexpr int kSCapU = 306, kSCapT = 512;
+constexpr int kM1CapU = 1228, kM1CapT = 2048;
+constexpr int kM2CapU = 4914, kM2CapT = 8192;
+constexpr int kLCapT = 32768;
+constexpr int kListsPerGroup = 5;   // X2, NEW, P, Q, STATE (the sixth list is the output slice)
+
+__host__ __device__ inline void next_level(int size, long long& trig, int& next_size) {
+    const long long mask = size - 1;
+    trig = (3 * mask + 4) / 5;                         // smallest fill with 5*fill >= 3*mask
+    const long long minused = trig > 50000 ? trig * 2 : trig * 4;
+    long long ns = kMinTable;
+    while (ns <= minused) ns <<= 1;
+    next_size = (int)(ns > (1ll << 30) ? (1ll << 30) : ns);
+}
 
 // Table length after `distinct` different keys were added to an empty set.
 __host__ __device__ inline int final_table_len(int distinct) {
-    long long size = kMinTable;
+    int size = kMinTable;
     for (;;) {
-        const long long mask = size - 1;
-        const long long trig = (3 * mask + 4) / 5;       // smallest fill with 5*fill >= 3*mask
-        if (distinct < trig) return (int)size;
-        const long long minused = trig > 50000 ? trig * 2 : trig * 4;
-        long long ns = kMinTable;
-        while (ns <= minused) ns <<= 1;
+        long long trig;
+        int ns;
+        next_level(size, trig, ns);
+        if (distinct < trig || size >= (1 << 30)) return size;
         size = ns;
-        if (size > (1ll << 30)) return (int)size;
     }
 }
 
-__host__ __device__ inline long long group_table_ints(int tbl_len, bool with_values) {
-    if (tbl_len == 0) return 0;
-    const long long small = tbl_len / 4 > kMinTable ? tbl_len / 4 : kMinTable;
-    return (long long)tbl_len + small + (with_values ? tbl_len : 0);
+__host__ __device__ inline int replay_class(int u, int tbl_len) {
+    if (tbl_len == 0) return kClassSorted;
+    if (u <= kSCapU) return kClassS;
+    if (u <= kM1CapU) return kClassM1;
+    if (u <= kM2CapU) return kClassM2;
+    if (tbl_len <= kLCapT) return kClassL;
+    return kClassXL;
+}
+
+// Global scratch ints of one replayed group.
+__host__ __device__ inline long long group_scratch_ints(int u, int tbl_len) {
+    const int c = replay_class(u, tbl_len);
+    if (c == kClassL) return (long long)kListsPerGroup * u;
+    if (c == kClassXL) return (long long)kListsPerGroup * u + tbl_len;
+    return 0;
 }
 
 __device__ __forceinline__ int warp_sum(int v) {
@@ -77,27 +130,98 @@ __device__ __forceinline__ int warp_incl_scan(int v, int lane) {
     return v;
 }
 
+// ---- teams -------------------------------------------------------------------
+struct WarpTeam {
+    static constexpr int kSize = 32;
+    static constexpr int kPerBlock = 8;
+    __device__ static int tid() { return threadIdx.x & 31; }
+    __device__ static int index_in_block() { return threadIdx.x >> 5; }
+    __device__ static void sync() { __syncwarp(); }
+    __device__ static bool any(bool p, int*) { return __any_sync(0xffffffffu, p); }
+    __device__ static int sum(int v, int*) { return warp_sum(v); }
+    __device__ static int max_of(int v, int*) { return warp_max(v); }
+    // rank of this thread among the flagged threads of the team, in thread order
+    __device__ static int rank(bool flag, int& total, int*) {
+        const unsigned b = __ballot_sync(0xffffffffu, flag);
+        total = __popc(b);
+        return __popc(b & ((1u << (threadIdx.x & 31)) - 1u));
+    }
+};
+
+template <int THREADS>
+struct BlockTeam {
+    static constexpr int kSize = THREADS;
+    static constexpr int kPerBlock = 1;
+    __device__ static int tid() { return threadIdx.x; }
+    __device__ static int index_in_block() { return 0; }
+    __device__ static void sync() { __syncthreads(); }
+    __device__ static bool any(bool p, int*) { return __syncthreads_or(p ? 1 : 0) != 0; }
+    __device__ static int sum(int v, int* scratch) {            // scratch: 33 ints of shared memory
+        v = warp_sum(v);
+        if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
+        __syncthreads();
+        int t = 0;
+        for (int w = 0; w < THREADS / 32; ++w) t += scratch[w];
+        __syncthreads();
+        return t;
+    }
+    __device__ static int max_of(int v, int* scratch) {
+        v = warp_max(v);
+        if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
+        __syncthreads();
+        int t = scratch[0];
+        for (int w = 1; w < THREADS / 32; ++w) t = max(t, scratch[w]);
+        __syncthreads();
+        return t;
+    }
+    __device__ static int rank(bool flag, int& total, int* scratch) {
+        const unsigned b = __ballot_sync(0xffffffffu, flag);
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+        if (lane == 0) scratch[warp] = __popc(b);
+        __syncthreads();
+        int before = 0, all = 0;
+        for (int w = 0; w < THREADS / 32; ++w) {
+            const int c = scratch[w];
+            if (w < warp) before += c;
+            all += c;
+        }
+        __syncthreads();
+        total = all;
+        return before + __popc(b & ((1u << lane) - 1u));
+    }
+};
+
+// Groups with many entries get a whole CTA, the others a warp: two launches of the same kernel,
+// each taking the groups that pass its filter (0 = all, 1 = at most kBigGroup entries, 2 = more).
+constexpr int kBigGroup = 1024;
+__device__ __forceinline__ bool group_passes(int filter, int entries) {
+    return filter == 0 || (filter == 1) == (entries <= kBigGroup);
+}
+
 // ---------------------------------------------------------------- pass 1: count
+template <class Team>
 __global__ void __launch_bounds__(256)
-svc_count_kernel(SvcProblem p, int words, int* __restrict__ counts, int* __restrict__ mode, int* __restrict__ tbl_len) {
+svc_count_kernel(SvcProblem p, int words, int filter, int* __restrict__ counts, int* __restrict__ mode,
+                 int* __restrict__ tbl_len) {
     extern __shared__ unsigned int sm_words[];
-    const int warps = blockDim.x >> 5;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    unsigned int* bm = sm_words + (size_t)warp * words;
-    for (int i = blockIdx.x * warps + warp; i < p.m_vec; i += gridDim.x * warps) {
+    __shared__ int red[33];
+    unsigned int* bm = sm_words + (size_t)Team::index_in_block() * words;
+    const int tid = Team::tid();
+    for (int i = blockIdx.x * Team::kPerBlock + Team::index_in_block(); i < p.m_vec; i += gridDim.x * Team::kPerBlock) {
         const int r0 = min(i * p.V, p.M), r1 = min(i * p.V + p.V, p.M);
         const int e0 = p.row_ptr[r0], e1 = p.row_ptr[r1];
+        if (!group_passes(filter, e1 - e0)) continue;
         if (e1 - e0 < words) {
-            for (int e = e0 + lane; e < e1; e += 32) {
+            for (int e = e0 + tid; e < e1; e += Team::kSize) {
                 const unsigned c = (unsigned)p.col_idx[e];
                 if (c < (unsigned)p.K) bm[c >> 5] = 0u;
             }
         } else {
-            for (int w = lane; w < words; w += 32) bm[w] = 0u;
+            for (int w = tid; w < words; w += Team::kSize) bm[w] = 0u;
         }
-        __syncwarp();
+        Team::sync();
         int cnt = 0, mx = -1, bad = 0;
-        for (int e = e0 + lane; e < e1; e += 32) {
+        for (int e = e0 + tid; e < e1; e += Team::kSize) {
             const int c = p.col_idx[e];
             if ((unsigned)c < (unsigned)p.K) {
                 const unsigned bit = 1u << (c & 31);
@@ -108,10 +232,10 @@ svc_count_kernel(SvcProblem p, int words, int* __restrict__ counts, int* __restr
                 bad = 1;
             }
         }
-        cnt = warp_sum(cnt);
-        mx = warp_max(mx);
-        bad = warp_max(bad);
-        if (lane == 0) {
+        cnt = Team::sum(cnt, red);
+        mx = Team::max_of(mx, red);
+        bad = Team::max_of(bad, red);
+        if (tid == 0) {
             counts[i] = cnt;
             const int len = final_table_len(cnt);
             const int replay = (mx >= len) ? 1 : 0;
@@ -119,25 +243,29 @@ svc_count_kernel(SvcProblem p, int words, int* __restrict__ counts, int* __restr
             tbl_len[i] = replay ? len : 0;
             if (bad) g_svc_bad_column = 1;
         }
-        __syncwarp();
+        Team::sync();
     }
 }
 
 // ---------------------------------------------------------------- scans (one CTA)
+// totals: [0] nvec, [1] scratch ints, [2..2+kNumClasses) groups per replay class
 __global__ void __launch_bounds__(1024)
 svc_scan_kernel(int m_vec, int* __restrict__ vec_ptr, const int* __restrict__ tbl_len, long long* __restrict__ tbl_off,
-                long long* __restrict__ totals, int with_values) {
+                long long* __restrict__ totals) {
     __shared__ long long sh_a[32], sh_b[32];
     __shared__ long long carry_a, carry_b;
+    __shared__ int hist[kNumClasses];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     if (threadIdx.x == 0) { carry_a = 0; carry_b = 0; }
+    if (threadIdx.x < kNumClasses) hist[threadIdx.x] = 0;
     __syncthreads();
     for (int base = 0; base < m_vec; base += 1024) {
         const int i = base + threadIdx.x;
         long long a = 0, b = 0;
         if (i < m_vec) {
             a = vec_ptr[i];
-            b = group_table_ints(tbl_len[i], with_values != 0);
+            b = group_scratch_ints((int)a, tbl_len[i]);
+            atomicAdd(&hist[replay_class((int)a, tbl_len[i])], 1);
         }
         long long ia = a, ib = b;
 #pragma unroll
@@ -174,37 +302,57 @@ svc_scan_kernel(int m_vec, int* __restrict__ vec_ptr, const int* __restrict__ tb
         tbl_off[m_vec] = carry_b;
         totals[0] = carry_a;
         totals[1] = carry_b;
+        for (int c = 0; c < kNumClasses; ++c) totals[2 + c] = hist[c];
     }
 }
 
 // ---------------------------------------------------------------- pass 2a: ascending order
+template <class Team>
 __global__ void __launch_bounds__(256)
-svc_emit_sorted_kernel(SvcProblem p, int words, const int* __restrict__ vec_ptr, const int* __restrict__ mode,
-                       int* __restrict__ out_col, __half* __restrict__ out_vals) {
+svc_emit_sorted_kernel(SvcProblem p, int words, int filter, const int* __restrict__ vec_ptr,
+                       const int* __restrict__ mode, int* __restrict__ out_col, __half* __restrict__ out_vals) {
     extern __shared__ unsigned int sm_words[];
-    const int warps = blockDim.x >> 5;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    unsigned int* bm = sm_words + (size_t)warp * words * 2;
+    __shared__ int red[33];
+    unsigned int* bm = sm_words + (size_t)Team::index_in_block() * words * 2;
     unsigned int* pre = bm + words;
-    for (int i = blockIdx.x * warps + warp; i < p.m_vec; i += gridDim.x * warps) {
+    const int tid = Team::tid();
+    for (int i = blockIdx.x * Team::kPerBlock + Team::index_in_block(); i < p.m_vec; i += gridDim.x * Team::kPerBlock) {
         if (mode[i] != 0) continue;
         const int r0 = min(i * p.V, p.M), r1 = min(i * p.V + p.V, p.M);
         const int e0 = p.row_ptr[r0], e1 = p.row_ptr[r1];
         const int base = vec_ptr[i];
-        if (e1 == e0) continue;
-        for (int w = lane; w < words; w += 32) bm[w] = 0u;
-        __syncwarp();
-        for (int e = e0 + lane; e < e1; e += 32) {
+        if (e1 == e0 || !group_passes(filter, e1 - e0)) continue;
+        for (int w = tid; w < words; w += Team::kSize) bm[w] = 0u;
+        Team::sync();
+        for (int e = e0 + tid; e < e1; e += Team::kSize) {
             const int c = p.col_idx[e];
             if ((unsigned)c < (unsigned)p.K) atomicOr(&bm[c >> 5], 1u << (c & 31));
         }
-        __syncwarp();
+        Team::sync();
         int running = 0;
-        for (int w0 = 0; w0 < words; w0 += 32) {
-            const int w = w0 + lane;
+        for (int w0 = 0; w0 < words; w0 += Team::kSize) {
+            const int w = w0 + tid;
             unsigned word = (w < words) ? bm[w] : 0u;
             const int pc = __popc(word);
-            const int incl = warp_incl_scan(pc, lane);
+            // exclusive prefix of pc over the team, in thread order
+            int incl = warp_incl_scan(pc, tid & 31);
+            int chunk_total;
+            if constexpr (Team::kSize == 32) {
+                chunk_total = __shfl_sync(0xffffffffu, incl, 31);
+            } else {
+                const int wp = tid >> 5;
+                if ((tid & 31) == 31) red[wp] = incl;
+                __syncthreads();
+                int before = 0, all = 0;
+                for (int x = 0; x < Team::kSize / 32; ++x) {
+                    const int c = red[x];
+                    if (x < wp) before += c;
+                    all += c;
+                }
+                __syncthreads();
+                incl += before;
+                chunk_total = all;
+            }
             int o = running + incl - pc;
             if (w < words) pre[w] = (unsigned)o;
             o += base;
@@ -213,206 +361,549 @@ svc_emit_sorted_kernel(SvcProblem p, int words, const int* __restrict__ vec_ptr,
                 out_col[o++] = w * 32 + b;
                 word &= word - 1;
             }
-            running += __shfl_sync(0xffffffffu, incl, 31);
+            running += chunk_total;
         }
         if (out_vals) {
-            __syncwarp();
-            for (int r = r0; r < r1; ++r) {
-                const int v = r - i * p.V;
-                for (int e = p.row_ptr[r] + lane; e < p.row_ptr[r + 1]; e += 32) {
-                    const int c = p.col_idx[e];
-                    if ((unsigned)c < (unsigned)p.K) {
-                        const int pos = (int)pre[c >> 5] + __popc(bm[c >> 5] & ((1u << (c & 31)) - 1u));
-                        out_vals[((int64_t)base + pos) * p.V + v] = p.vals[e];
-                    }
+            Team::sync();
+            // all entries of the group, flat; the matrix row of entry e is found by walking the (at most V) row ends
+            for (int e = e0 + tid; e < e1; e += Team::kSize) {
+                int r = r0;
+                while (r + 1 < r1 && e >= p.row_ptr[r + 1]) ++r;
+                const int c = p.col_idx[e];
+                if ((unsigned)c < (unsigned)p.K) {
+                    const int pos = (int)pre[c >> 5] + __popc(bm[c >> 5] & ((1u << (c & 31)) - 1u));
+                    out_vals[((int64_t)base + pos) * p.V + (r - i * p.V)] = p.vals[e];
                 }
             }
         }
-        __syncwarp();
+        Team::sync();
     }
 }
 
 // ---------------------------------------------------------------- pass 2b: hash-table replay
-// Slot that `key` occupies, or the first free slot on its probe path.
-__device__ __forceinline__ int probe_slot(const int* tab, unsigned mask, int key) {
-    unsigned perturb = (unsigned)key;
-    unsigned i = (unsigned)key & mask;
-    for (;;) {
-        const unsigned window = (i + kLinearProbes <= mask) ? kLinearProbes : 0;
-        for (unsigned s = i; s <= i + window; ++s) {
+struct Probe {            // position on a key's probe path
+    unsigned i;           // start of the current window
+    unsigned w;           // offset inside the window
+    unsigned perturb;
+};
+__device__ __forceinline__ Probe probe_begin(int key, unsigned mask) {
+    Probe p;
+    p.i = (unsigned)key & mask; p.w = 0; p.perturb = (unsigned)key;
+    return p;
+}
+// Returns true when the step was a jump to a new window.
+__device__ __forceinline__ bool probe_advance(Probe& p, unsigned mask) {
+    const unsigned window = (p.i + kLinearProbes <= mask) ? kLinearProbes : 0;
+    if (p.w < window) {
+        ++p.w;
+        return false;
+    }
+    p.perturb >>= kPerturbShift;
+    p.i = (p.i * 5u + 1u + p.perturb) & mask;
+    p.w = 0;
+    return true;
+}
+// Table of KEYS (-1 = free): slot holding `key`, or -1 when the path reaches a free slot first.
+// Every probe loop is bounded (a table is never more than 60 % full, so a free slot is near).
+__device__ __forceinline__ int find_key(const int* tab, unsigned mask, int key) {
+    Probe p = probe_begin(key, mask);
+    for (unsigned n = 0; n <= 8u * mask + 64u; ++n) {
+        const int e = tab[p.i + p.w];
+        if (e == key) return (int)(p.i + p.w);
+        if (e == -1) return -1;
+        probe_advance(p, mask);
+    }
+    return -1;
+}
+// Same, returning the first free slot when the key is absent (sequential insertion).
+__device__ __forceinline__ int find_slot(const int* tab, unsigned mask, int key) {
+    Probe p = probe_begin(key, mask);
+    for (unsigned n = 0; n <= 8u * mask + 64u; ++n) {
+        const int e = tab[p.i + p.w];
+        if (e == key || e == -1) return (int)(p.i + p.w);
+        probe_advance(p, mask);
+    }
+    return (int)(p.i + p.w);
+}
+
+// STATE word of one element during a level: bits 0..23 window start, 24..27 offset, 28..30 jumps, 31 settled.
+// perturb is recomputed as key >> (5 * jumps); jumps saturates at 7 (perturb is 0 from the 7th jump on for keys < 2^31).
+__device__ __forceinline__ unsigned pack_state(const Probe& p, unsigned jumps, bool settled) {
+    return (p.i & 0xffffffu) | (p.w << 24) | (min(jumps, 7u) << 28) | (settled ? 0x80000000u : 0u);
+}
+
+struct ReplayBuffers {
+    int* table;     // cap ints
+    int* lists[6];  // six lists of u ints: two of them alternate as the ordered list (one is the output slice)
+};
+
+// Ordered extraction: keys of `tab` in slot order into dst; returns how many.  With seq != null the
+// table holds sequence numbers (kEmptyPrio = free) and is rewritten in place to hold keys (-1 = free).
+template <class Team>
+__device__ int extract_ordered(int* tab, int size, const int* seq, int* dst, int* red) {
+    const int tid = Team::tid();
+    int n = 0;
+    for (int s0 = 0; s0 < size; s0 += Team::kSize) {
+        const int s = s0 + tid;
+        int key = -1;
+        if (s < size) {
             const int e = tab[s];
-            if (e == -1 || e == key) return (int)s;
+            if (seq) {
+                key = (e == kEmptyPrio) ? -1 : seq[e];
+                tab[s] = key;
+            } else {
+                key = e;
+            }
         }
-        perturb >>= kPerturbShift;
-        i = (i * 5u + 1u + perturb) & mask;
+        int total;
+        const int rk = Team::rank(key != -1, total, red);
+        if (key != -1) dst[n + rk] = key;
+        n += total;
     }
-}
-
-__global__ void __launch_bounds__(256)
-svc_emit_replay_kernel(SvcProblem p, const int* __restrict__ vec_ptr, const int* __restrict__ mode,
-                       const int* __restrict__ tbl_len, const long long* __restrict__ tbl_off, int* __restrict__ tables,
-                       int* __restrict__ out_col, __half* __restrict__ out_vals) {
-    const int warps = blockDim.x >> 5;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int i = blockIdx.x * warps + warp; i < p.m_vec; i += gridDim.x * warps) {
-        if (mode[i] == 0) continue;
-        const int r0 = min(i * p.V, p.M), r1 = min(i * p.V + p.V, p.M);
-        const int base = vec_ptr[i];
-        int* list = out_col + base;                 // current ordered list lives in the output slice
-        const int cap = tbl_len[i];
-        int* reg0 = tables + tbl_off[i];            // holds the final table
-        int* reg1 = reg0 + cap;                     // holds the table one growth step earlier
-        const int small = cap / 4 > kMinTable ? cap / 4 : kMinTable;
-        int* pos_tab = reg1 + small;                // slot -> position, only with values
-        int cur_len = 0;
-        int* tab = reg0;
-        unsigned mask = kMinTable - 1;
-        for (int r = r0; r < r1; ++r) {
-            const int rs = p.row_ptr[r], rlen = p.row_ptr[r + 1] - rs;
-            const int total = cur_len + rlen;
-            // a fresh 8-slot table; regions alternate so that a table of length `cap` lands in reg0
-            int size = kMinTable;
-            int used = 0;
-            mask = kMinTable - 1;
-            // parity of the number of growth steps still possible decides the start region
-            int steps_to_cap = 0;
-            for (int s = kMinTable; s < cap; s <<= 2) ++steps_to_cap;
-            tab = (steps_to_cap & 1) ? reg1 : reg0;
-            if (lane < kMinTable) tab[lane] = -1;
-            __syncwarp();
-            int t = 0;
-            for (;;) {
-                int grow = 0;
-                if (lane == 0) {
-                    while (t < total) {
-                        const int key = (t < cur_len) ? list[t] : p.col_idx[rs + t - cur_len];
-                        ++t;
-                        if ((unsigned)key >= (unsigned)p.K) continue;
-                        const int s = probe_slot(tab, mask, key);
-                        if (tab[s] == key) continue;
-                        tab[s] = key;
-                        ++used;
-                        if ((long long)used * 5 >= (long long)mask * 3) { grow = 1; break; }
-                    }
-                }
-                t = __shfl_sync(0xffffffffu, t, 0);
-                used = __shfl_sync(0xffffffffu, used, 0);
-                grow = __shfl_sync(0xffffffffu, grow, 0);
-                if (!grow) break;
-                const long long minused = used > 50000 ? (long long)used * 2 : (long long)used * 4;
-                int nsize = kMinTable;
-                while (nsize <= minused) nsize <<= 1;
-                int* ntab = (tab == reg0) ? reg1 : reg0;
-                if (nsize > cap) { nsize = cap; }     // cannot happen when counts are consistent
-                for (int s = lane; s < nsize; s += 32) ntab[s] = -1;
-                __syncwarp();
-                if (lane == 0) {
-                    const unsigned nmask = (unsigned)nsize - 1u;
-                    for (int s = 0; s < size; ++s) {
-                        const int key = tab[s];
-                        if (key != -1) ntab[probe_slot(ntab, nmask, key)] = key;
-                    }
-                }
-                __syncwarp();
-                tab = ntab;
-                size = nsize;
-                mask = (unsigned)nsize - 1u;
-            }
-            // ordered extraction into the output slice
-            int n = 0;
-            for (int s0 = 0; s0 < size; s0 += 32) {
-                const int s = s0 + lane;
-                const int key = (s < size) ? tab[s] : -1;
-                const unsigned bal = __ballot_sync(0xffffffffu, key != -1);
-                if (key != -1) list[n + __popc(bal & ((1u << lane) - 1u))] = key;
-                n += __popc(bal);
-            }
-            cur_len = n;
-            __syncwarp();
-        }
-        if (out_vals && cur_len > 0) {
-            const int size = (int)mask + 1;
-            int n = 0;
-            for (int s0 = 0; s0 < size; s0 += 32) {
-                const int s = s0 + lane;
-                const int key = (s < size) ? tab[s] : -1;
-                const unsigned bal = __ballot_sync(0xffffffffu, key != -1);
-                if (s < size) pos_tab[s] = n + __popc(bal & ((1u << lane) - 1u));
-                n += __popc(bal);
-            }
-            __syncwarp();
-            for (int r = r0; r < r1; ++r) {
-                const int v = r - i * p.V;
-                for (int e = p.row_ptr[r] + lane; e < p.row_ptr[r + 1]; e += 32) {
-                    const int c = p.col_idx[e];
-                    if ((unsigned)c < (unsigned)p.K) {
-                        const int pos = pos_tab[probe_slot(tab, mask, c)];
-                        out_vals[((int64_t)base + pos) * p.V + v] = p.vals[e];
-                    }
-                }
-            }
-        }
-        __syncwarp();
-    }
-}
-
-int device_sm_count() {
-    int dev = 0, n = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    Team::sync();
     return n;
+}
+
+// Fill at which the 128-slot table grows to 512: up to here one thread inserts sequentially
+// (three tiny tables are not worth a team-wide pass each).
+constexpr int kSeqPrefix = 77;
+
+// Sequential replay by one thread (used when a matrix row lists a column twice; rare).  tab holds keys.
+__device__ int replay_sequential(const SvcProblem& p, int r0, int r1, int* tab, int cap, int* xa, int* xb, int* tmp) {
+    int n_cur = 0;
+    int* x = xa;
+    int* xn = xb;
+    unsigned mask = kMinTable - 1;
+    for (int r = r0; r < r1; ++r) {
+        const int rs = p.row_ptr[r], rlen = p.row_ptr[r + 1] - rs;
+        int size = kMinTable, used = 0;
+        mask = kMinTable - 1;
+        for (int s = 0; s < size; ++s) tab[s] = -1;
+        for (int t = 0; t < n_cur + rlen; ++t) {
+            const int key = (t < n_cur) ? x[t] : p.col_idx[rs + t - n_cur];
+            if ((unsigned)key >= (unsigned)p.K) continue;
+            const int s = find_slot(tab, mask, key);
+            if (tab[s] == key) continue;
+            tab[s] = key;
+            ++used;
+            if ((long long)used * 5 >= (long long)mask * 3) {
+                long long trig; int nsize;
+                next_level(size, trig, nsize);
+                if (nsize > cap) nsize = cap;
+                int cnt = 0;
+                for (int q = 0; q < size; ++q) if (tab[q] != -1) tmp[cnt++] = tab[q];
+                for (int q = 0; q < nsize; ++q) tab[q] = -1;
+                const unsigned nmask = (unsigned)nsize - 1u;
+                for (int q = 0; q < cnt; ++q) tab[find_slot(tab, nmask, tmp[q])] = tmp[q];
+                size = nsize; mask = nmask;
+            }
+        }
+        int cnt = 0;
+        for (int q = 0; q < size; ++q) if (tab[q] != -1) xn[cnt++] = tab[q];
+        n_cur = cnt;
+        int* t2 = x; x = xn; xn = t2;
+    }
+    return (int)mask;      // the ordered list is in `x` = xa if (r1-r0) is even else xb; caller arranges parity
+}
+
+template <class Team>
+__device__ void replay_group(const SvcProblem& p, int i, int u_final, int cap, int base, ReplayBuffers bufs,
+                             int* __restrict__ out_col, __half* __restrict__ out_vals, int* red) {
+    const int tid = Team::tid();
+    const int r0 = min(i * p.V, p.M), r1 = min(i * p.V + p.V, p.M);
+    const int n_rebuilds = r1 - r0;
+    int* const tab = bufs.table;
+    // the ordered list alternates between two buffers; arrange that the last rebuild writes the output slice
+    int* const out_slice = out_col + base;
+    int* x = (n_rebuilds & 1) ? bufs.lists[0] : out_slice;      // list before the first rebuild (empty)
+    int* xn = (n_rebuilds & 1) ? out_slice : bufs.lists[0];     // written by the first rebuild
+    int* const fresh = bufs.lists[1];                           // NEW: columns of the row not yet in the set
+    int* seq = bufs.lists[2];                                   // insertion sequence of the current level
+    int* seq_other = bufs.lists[3];
+    unsigned* const state = reinterpret_cast<unsigned*>(bufs.lists[4]);
+
+    int n_cur = 0;
+    unsigned mask_prev = kMinTable - 1;
+    if (tid < kMinTable) tab[tid] = -1;
+    Team::sync();
+    bool duplicate = false;
+    PROF_DECL
+
+    for (int r = r0; r < r1 && !duplicate; ++r) {
+        const int rs = p.row_ptr[r], rlen = p.row_ptr[r + 1] - rs;
+        // ---- columns of this row that are not in the current set, in row order
+        int n_new = 0;
+        for (int t0 = 0; t0 < rlen; t0 += Team::kSize) {
+            const int t = t0 + tid;
+            const int key = (t < rlen) ? p.col_idx[rs + t] : -1;
+            const bool isnew = (t < rlen) && (unsigned)key < (unsigned)p.K && find_key(tab, mask_prev, key) < 0;
+            int total;
+            const int rk = Team::rank(isnew, total, red);
+            if (isnew && n_cur + n_new + rk < u_final) fresh[n_new + rk] = key;
+            n_new += total;
+        }
+        Team::sync();
+        const int n_total = n_cur + n_new;
+        if (n_total > u_final) { duplicate = true; break; }     // only possible when the row repeats a column
+        PROF_MARK(0)
+
+        // ---- replay  set(list)  for the sequence  D = x[0..n_cur) ++ fresh[0..n_new)
+        // (a) the first 77 elements (tables of 8, 32, 128 slots) by one thread, storing keys
+        int size = kMinTable, e_len = 0;
+        unsigned mask = kMinTable - 1;
+        {
+            int result = 0;                     // bit 31: duplicate met; low bits: table length reached
+            if (tid == 0) {
+                int sz = kMinTable, used = 0;
+                unsigned mk = kMinTable - 1;
+                bool dup = false;
+                for (int s = 0; s < sz; ++s) tab[s] = -1;
+                const int n_seq = min(n_total, kSeqPrefix);
+                for (int t = 0; t < n_seq; ++t) {
+                    const int key = (t < n_cur) ? x[t] : fresh[t - n_cur];
+                    const int sl = find_slot(tab, mk, key);
+                    if (tab[sl] == key) { dup = true; break; }
+                    tab[sl] = key;
+                    ++used;
+                    if (used * 5 >= (int)mk * 3 && sz < 128) {
+                        int cnt = 0;
+                        for (int q = 0; q < sz; ++q) if (tab[q] != -1) seq_other[cnt++] = tab[q];
+                        sz *= 4;
+                        mk = (unsigned)sz - 1u;
+                        for (int q = 0; q < sz; ++q) tab[q] = -1;
+                        for (int q = 0; q < cnt; ++q) tab[find_slot(tab, mk, seq_other[q])] = seq_other[q];
+                    }
+                }
+                result = sz | (dup ? 0x40000000 : 0);
+            }
+            result = Team::max_of(result, red);         // broadcast (other threads hold 0)
+            Team::sync();                               // thread 0's table writes are visible to the team
+            if (result & 0x40000000) { duplicate = true; break; }
+            size = result & 0xffff;
+            mask = (unsigned)size - 1u;
+        }
+        PROF_MARK(1)
+        if (n_total >= kSeqPrefix) {
+            // the 77th insertion filled the 128-slot table: it grows to 512 and the team takes over
+            e_len = extract_ordered<Team>(tab, size, nullptr, seq, red);
+            size = 512 > cap ? cap : 512;
+            // (b) remaining levels in parallel: first come, first served with atomicMin on sequence numbers
+            for (;;) {
+                long long trig_ll; int next_size;
+                next_level(size, trig_ll, next_size);
+                const int trig = (int)(trig_ll > 0x7fffffff ? 0x7fffffff : trig_ll);
+                const int n_l = min(trig, n_total);
+                mask = (unsigned)size - 1u;
+                for (int s = tid; s < size; s += Team::kSize) tab[s] = kEmptyPrio;
+                for (int q = e_len + tid; q < n_l; q += Team::kSize) seq[q] = (q < n_cur) ? x[q] : fresh[q - n_cur];
+                Team::sync();
+                for (int q = tid; q < n_l; q += Team::kSize) state[q] = pack_state(probe_begin(seq[q], mask), 0, false);
+                const int first_new = max(e_len, n_cur);
+                PROF_MARK(2)
+                bool dup_here = false;          // also raised when a bound below is hit: the group is then redone sequentially
+                for (int round = 0;; ++round) {
+                    bool changed = false;
+                    if (round > n_l + 16) dup_here = true;
+                    for (int q = tid; q < n_l; q += Team::kSize) {
+                        unsigned st = state[q];
+                        const int key = seq[q];
+                        Probe pr;
+                        unsigned jumps = (st >> 28) & 7u;
+                        pr.i = st & 0xffffffu; pr.w = (st >> 24) & 15u;
+                        pr.perturb = (jumps >= 7u) ? 0u : ((unsigned)key >> (kPerturbShift * jumps));
+                        bool settled = (st >> 31) != 0;
+                        if (settled) {
+                            if (tab[pr.i + pr.w] == q) continue;
+                            settled = false;                         // displaced by an earlier element: move on
+                            if (probe_advance(pr, mask)) ++jumps;
+                            changed = true;
+                        }
+                        for (unsigned tries = 0;; ++tries) {
+                            const int old = atomicMin(&tab[pr.i + pr.w], q);
+                            if (old > q) { settled = true; changed = true; break; }
+                            if ((q >= first_new && seq[old] == key) || tries > 8u * mask + 64u) { dup_here = true; settled = true; break; }
+                            if (probe_advance(pr, mask)) ++jumps;
+                        }
+                        state[q] = pack_state(pr, jumps, settled);
+                    }
+                    Team::sync();
+                    if (!Team::any(changed && !dup_here, red)) break;
+                }
+                if (Team::any(dup_here, red)) { duplicate = true; break; }
+                PROF_MARK(3)
+                if (n_total < trig) {
+                    // no further growth: this table is final; keys in place, ordered list out
+                    n_cur = extract_ordered<Team>(tab, size, seq, xn, red);
+                    break;
+                }
+                e_len = extract_ordered<Team>(tab, size, seq, seq_other, red);
+                int* t2 = seq; seq = seq_other; seq_other = t2;
+                size = (next_size > cap) ? cap : next_size;
+            }
+            if (duplicate) break;
+        } else {
+            n_cur = extract_ordered<Team>(tab, size, nullptr, xn, red);
+        }
+        int* t2 = x; x = xn; xn = t2;
+        mask_prev = mask;
+        PROF_MARK(4)
+    }
+
+    if (duplicate) {
+        // rare: fall back to the sequential replay of the whole group by one thread
+        int* xa = (n_rebuilds & 1) ? bufs.lists[0] : out_slice;
+        int* xb = (n_rebuilds & 1) ? out_slice : bufs.lists[0];
+        int m = 0;
+        if (tid == 0) m = replay_sequential(p, r0, r1, tab, cap, xa, xb, bufs.lists[2]);
+        Team::sync();
+        mask_prev = (unsigned)Team::max_of(m, red);
+        n_cur = u_final;
+    }
+    // here: out_slice holds the ordered list, tab holds its keys at their slots
+    if (out_vals && n_cur > 0) {
+        const int size = (int)mask_prev + 1;
+        int n = 0;
+        for (int s0 = 0; s0 < size; s0 += Team::kSize) {        // slot -> position
+            const int s = s0 + tid;
+            const int key = (s < size) ? tab[s] : -1;
+            int total;
+            const int rk = Team::rank(key != -1, total, red);
+            if (key != -1) state[n + rk] = (unsigned)s;          // position -> slot (ascending), searched below
+            n += total;
+        }
+        Team::sync();
+        const int e0 = p.row_ptr[r0], e1 = p.row_ptr[r1];
+        for (int e = e0 + tid; e < e1; e += Team::kSize) {
+            int r = r0;
+            while (r + 1 < r1 && e >= p.row_ptr[r + 1]) ++r;
+            const int c = p.col_idx[e];
+            if ((unsigned)c >= (unsigned)p.K) continue;
+            const int s = find_key(tab, mask_prev, c);
+            if (s < 0) continue;
+            // position of slot s = number of occupied slots before it: binary search in the slot list
+            int lo = 0, hi = n - 1;
+            while (lo < hi) {
+                const int mid = (lo + hi) >> 1;
+                if ((int)state[mid] < s) lo = mid + 1; else hi = mid;
+            }
+            out_vals[((int64_t)base + lo) * p.V + (r - i * p.V)] = p.vals[e];
+        }
+    }
+    Team::sync();
+    PROF_MARK(5)
+    PROF_FLUSH(replay_class(u_final, cap))
+}
+
+template <class Team, int CLASS>
+__global__ void __launch_bounds__(Team::kSize * Team::kPerBlock, 1)
+svc_emit_replay_kernel(SvcProblem p, const int* __restrict__ vec_ptr, const int* __restrict__ tbl_len,
+                       const long long* __restrict__ tbl_off, int* __restrict__ scratch, int* __restrict__ out_col,
+                       __half* __restrict__ out_vals, int smem_table_ints, int smem_list_ints) {
+    extern __shared__ int sm_ints[];
+    __shared__ int red[33];
+    const int per_team = smem_table_ints + kListsPerGroup * smem_list_ints;
+    int* mine = sm_ints + (size_t)Team::index_in_block() * per_team;
+    for (int i = blockIdx.x * Team::kPerBlock + Team::index_in_block(); i < p.m_vec; i += gridDim.x * Team::kPerBlock) {
+        const int base = vec_ptr[i];
+        const int u = vec_ptr[i + 1] - base;
+        const int cap = tbl_len[i];
+        if (replay_class(u, cap) != CLASS) continue;
+        ReplayBuffers b;
+        if (CLASS == kClassS || CLASS == kClassM1 || CLASS == kClassM2) {
+            b.table = mine;
+            for (int l = 0; l < kListsPerGroup; ++l) b.lists[l] = mine + smem_table_ints + l * smem_list_ints;
+        } else {
+            int* g = scratch + tbl_off[i];
+            for (int l = 0; l < kListsPerGroup; ++l) b.lists[l] = g + (size_t)l * u;
+            b.table = (CLASS == kClassL) ? mine : g + (size_t)kListsPerGroup * u;
+        }
+        replay_group<Team>(p, i, u, cap, base, b, out_col, out_vals, red);
+    }
+}
+
+int device_sm_count() { return current_device_sm_count(); }
+
+// Side streams so that launches working on disjoint groups overlap (fork from / join into the caller's stream).
+constexpr int kAuxStreams = 5;
+struct Aux {
+    cudaStream_t stream[kAuxStreams];
+    cudaEvent_t fork, join[kAuxStreams];
+    bool ready = false;
+};
+std::mutex g_aux_mu;                 // serialises enqueueing through the shared events
+Aux g_aux[64];
+
+Aux* aux_for_device() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    Aux& a = g_aux[dev];
+    if (!a.ready) {
+        for (int k = 0; k < kAuxStreams; ++k) {
+            if (cudaStreamCreateWithFlags(&a.stream[k], cudaStreamNonBlocking) != cudaSuccess) return nullptr;
+            if (cudaEventCreateWithFlags(&a.join[k], cudaEventDisableTiming) != cudaSuccess) return nullptr;
+        }
+        if (cudaEventCreateWithFlags(&a.fork, cudaEventDisableTiming) != cudaSuccess) return nullptr;
+        a.ready = true;
+    }
+    return &a;
+}
+
+struct Fork {
+    Aux* aux;
+    cudaStream_t main;
+    int used = 0;
+    cudaError_t err = cudaSuccess;
+    Fork(Aux* a, cudaStream_t m) : aux(a), main(m) {
+        if (aux) err = cudaEventRecord(aux->fork, main);
+    }
+    // stream for the next independent launch (the caller's stream when side streams are unavailable)
+    cudaStream_t next() {
+        if (!aux || used >= kAuxStreams || err != cudaSuccess) return main;
+        cudaStream_t s = aux->stream[used++];
+        err = cudaStreamWaitEvent(s, aux->fork, 0);
+        return err == cudaSuccess ? s : main;
+    }
+    cudaError_t join() {
+        if (!aux) return err;
+        for (int k = 0; k < used && err == cudaSuccess; ++k) {
+            err = cudaEventRecord(aux->join[k], aux->stream[k]);
+            if (err == cudaSuccess) err = cudaStreamWaitEvent(main, aux->join[k], 0);
+        }
+        return err;
+    }
+};
+
+template <class Team, int CLASS>
+cudaError_t launch_replay(const SvcProblem& p, const SvcScratch& s, int* out_col, __half* out_vals, long long groups,
+                          int table_ints, int list_ints, cudaStream_t stream) {
+    if (groups <= 0) return cudaSuccess;
+    auto kern = svc_emit_replay_kernel<Team, CLASS>;
+    const size_t smem = (size_t)Team::kPerBlock * (table_ints + (size_t)kListsPerGroup * list_ints) * sizeof(int);
+    static DeviceOnce once;
+    if (!once.done()) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        // without this the driver may size the shared-memory carve-out for a single resident block
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        if (e != cudaSuccess) return e;
+        once.mark();
+    }
+    const int sms = device_sm_count();
+    long long want = (groups + Team::kPerBlock - 1) / Team::kPerBlock;
+    // every block scans all groups for its class: a few blocks per SM are enough
+    const long long cap_blocks = (long long)sms * (smem > 100 * 1024 ? 1 : (smem > 40 * 1024 ? 3 : 6));
+    int grid = (int)(want < cap_blocks ? want : cap_blocks);
+    if (grid < 1) grid = 1;
+#ifdef SVC_PROFILE
+    {
+        int nb = -1;
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, kern, Team::kSize * Team::kPerBlock, smem);
+        printf("replay class %d: groups %lld grid %d smem %zu occupancy %d blocks/SM\n", CLASS, groups, grid, smem, nb);
+    }
+#endif
+    kern<<<grid, Team::kSize * Team::kPerBlock, smem, stream>>>(p, s.vec_ptr, s.tbl_len, s.tbl_off, s.tables, out_col,
+                                                                 out_vals, table_ints, list_ints);
+    return cudaGetLastError();
+}
+
+template <class Kern>
+cudaError_t allow_big_smem(Kern kern, DeviceOnce& once, int bytes) {
+    if (once.done()) return cudaSuccess;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    if (e == cudaSuccess) once.mark();
+    return e;
 }
 
 }  // namespace
 
-cudaError_t svc_count_and_scan(const SvcProblem& p, const SvcScratch& s, bool with_values, cudaStream_t stream) {
+cudaError_t svc_count_and_scan(const SvcProblem& p, const SvcScratch& s, bool /*with_values*/, cudaStream_t stream) {
     if (p.m_vec > 0) {
         const int words = (p.K + 31) / 32;
-        int warps = 8;
-        while (warps > 1 && (size_t)warps * words * 4 > 160 * 1024) warps >>= 1;
-        const size_t smem = (size_t)warps * words * 4;
-        cudaError_t ea = cudaFuncSetAttribute(svc_count_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        if (ea != cudaSuccess) return ea;
         const int sms = device_sm_count();
-        int grid = (p.m_vec + warps - 1) / warps;
-        const int cap = sms * 8;
-        if (grid > cap) grid = cap;
-        svc_count_kernel<<<grid, warps * 32, smem, stream>>>(p, words, s.vec_ptr, s.mode, s.tbl_len);
-        cudaError_t e = cudaGetLastError();
+        static DeviceOnce once_block, once_warp;
+        cudaError_t e = allow_big_smem(svc_count_kernel<BlockTeam<256>>, once_block, 200 * 1024);
+        if (e == cudaSuccess) e = allow_big_smem(svc_count_kernel<WarpTeam>, once_warp, 200 * 1024);
+        if (e != cudaSuccess) return e;
+        const size_t warp_smem = (size_t)WarpTeam::kPerBlock * words * 4;
+        if (p.m_vec <= 16 * sms || warp_smem > 200 * 1024) {
+            // few groups (or bitmaps too large for eight per block): one CTA per group
+            const int grid = p.m_vec < sms * 16 ? p.m_vec : sms * 16;
+            svc_count_kernel<BlockTeam<256>><<<grid, 256, (size_t)words * 4, stream>>>(p, words, 0, s.vec_ptr, s.mode, s.tbl_len);
+            e = cudaGetLastError();
+        } else {
+            std::lock_guard<std::mutex> lk(g_aux_mu);
+            Fork f(aux_for_device(), stream);
+            int grid = (p.m_vec + WarpTeam::kPerBlock - 1) / WarpTeam::kPerBlock;
+            if (grid > sms * 8) grid = sms * 8;
+            svc_count_kernel<WarpTeam><<<grid, 256, warp_smem, f.next()>>>(p, words, 1, s.vec_ptr, s.mode, s.tbl_len);
+            svc_count_kernel<BlockTeam<256>><<<sms * 4, 256, (size_t)words * 4, f.next()>>>(p, words, 2, s.vec_ptr, s.mode, s.tbl_len);
+            e = cudaGetLastError();
+            if (e == cudaSuccess) e = f.join();
+        }
         if (e != cudaSuccess) return e;
     }
-    svc_scan_kernel<<<1, 1024, 0, stream>>>(p.m_vec, s.vec_ptr, s.tbl_len, s.tbl_off, s.totals, with_values ? 1 : 0);
+    svc_scan_kernel<<<1, 1024, 0, stream>>>(p.m_vec, s.vec_ptr, s.tbl_len, s.tbl_off, s.totals);
     return cudaGetLastError();
 }
 
-cudaError_t svc_emit(const SvcProblem& p, const SvcScratch& s, int* out_col, __half* out_vals, cudaStream_t stream) {
+cudaError_t svc_emit(const SvcProblem& p, const SvcScratch& s, const long long* class_groups, int* out_col,
+                     __half* out_vals, cudaStream_t stream) {
     if (p.m_vec == 0) return cudaSuccess;
     const int sms = device_sm_count();
-    {
-        const int words = (p.K + 31) / 32;
-        int warps = 8;
-        while (warps > 1 && (size_t)warps * words * 8 > 200 * 1024) warps >>= 1;
-        const size_t smem = (size_t)warps * words * 8;
-        cudaError_t ea =
-            cudaFuncSetAttribute(svc_emit_sorted_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 208 * 1024);
-        if (ea != cudaSuccess) return ea;
-        int grid = (p.m_vec + warps - 1) / warps;
-        if (grid > sms * 8) grid = sms * 8;
-        svc_emit_sorted_kernel<<<grid, warps * 32, smem, stream>>>(p, words, s.vec_ptr, s.mode, out_col, out_vals);
-        cudaError_t e = cudaGetLastError();
+    const int words = (p.K + 31) / 32;
+    static DeviceOnce once_block, once_warp;
+    cudaError_t e = allow_big_smem(svc_emit_sorted_kernel<BlockTeam<256>>, once_block, 208 * 1024);
+    if (e == cudaSuccess) e = allow_big_smem(svc_emit_sorted_kernel<WarpTeam>, once_warp, 208 * 1024);
+    if (e != cudaSuccess) return e;
+
+    std::lock_guard<std::mutex> lk(g_aux_mu);
+    Fork f(aux_for_device(), stream);
+    if (class_groups[kClassSorted] > 0) {
+        const size_t warp_smem = (size_t)WarpTeam::kPerBlock * words * 8;
+        if (p.m_vec <= 16 * sms || warp_smem > 200 * 1024) {
+            const int grid = p.m_vec < sms * 16 ? p.m_vec : sms * 16;
+            svc_emit_sorted_kernel<BlockTeam<256>><<<grid, 256, (size_t)words * 8, stream>>>(p, words, 0, s.vec_ptr, s.mode, out_col, out_vals);
+        } else {
+            int grid = (p.m_vec + WarpTeam::kPerBlock - 1) / WarpTeam::kPerBlock;
+            if (grid > sms * 8) grid = sms * 8;
+            svc_emit_sorted_kernel<WarpTeam><<<grid, 256, warp_smem, stream>>>(p, words, 1, s.vec_ptr, s.mode, out_col, out_vals);
+            svc_emit_sorted_kernel<BlockTeam<256>><<<sms * 2, 256, (size_t)words * 8, f.next()>>>(p, words, 2, s.vec_ptr, s.mode, out_col, out_vals);
+        }
+        e = cudaGetLastError();
         if (e != cudaSuccess) return e;
     }
-    {
-        const int warps = 4;
-        int grid = (p.m_vec + warps - 1) / warps;
-        if (grid > sms * 16) grid = sms * 16;
-        svc_emit_replay_kernel<<<grid, warps * 32, 0, stream>>>(p, s.vec_ptr, s.mode, s.tbl_len, s.tbl_off, s.tables,
-                                                                out_col, out_vals);
-        cudaError_t e = cudaGetLastError();
-        if (e != cudaSuccess) return e;
-    }
-    return cudaSuccess;
+    // the largest groups first: they are the critical path
+    e = launch_replay<BlockTeam<1024>, kClassXL>(p, s, out_col, out_vals, class_groups[kClassXL], 0, 0, f.next());
+    if (e == cudaSuccess)
+        e = launch_replay<BlockTeam<1024>, kClassL>(p, s, out_col, out_vals, class_groups[kClassL], kLCapT, 0, f.next());
+    if (e == cudaSuccess)
+        e = launch_replay<BlockTeam<512>, kClassM2>(p, s, out_col, out_vals, class_groups[kClassM2], kM2CapT, kM2CapU + 2, f.next());
+    if (e == cudaSuccess)
+        e = launch_replay<BlockTeam<256>, kClassM1>(p, s, out_col, out_vals, class_groups[kClassM1], kM1CapT, kM1CapU + 4, f.next());
+    if (e == cudaSuccess)
+        e = launch_replay<WarpTeam, kClassS>(p, s, out_col, out_vals, class_groups[kClassS], kSCapT, kSCapU + 2, stream);
+    if (e != cudaSuccess) return e;
+    return f.join();
 }
+
+#ifdef SVC_PROFILE
+extern "C" void svc_profile_dump() {
+    unsigned long long h[64];
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(h, g_svc_prof, sizeof h);
+    const char* names[6] = {"new", "seqprefix", "level-setup", "rounds", "extract", "values"};
+    for (int c = 1; c < 6; ++c) {
+        if (!h[c * 8 + 7]) continue;
+        printf("class %d groups %llu:", c, h[c * 8 + 7]);
+        for (int k = 0; k < 6; ++k) printf(" %s=%.1fus", names[k], h[c * 8 + k] / 1.9e3 / (double)h[c * 8 + 7]);
+        printf("  (per group)\n");
+    }
+    unsigned long long z[64] = {0};
+    cudaMemcpyToSymbol(g_svc_prof, z, sizeof z);
+}
+#endif
 
 cudaError_t svc_read_and_clear_bad_column_flag(int* flag, cudaStream_t stream) {
     cudaError_t e = cudaMemcpyFromSymbolAsync(flag, g_svc_bad_column, sizeof(int), 0, cudaMemcpyDeviceToHost, stream);

@@ -28,16 +28,18 @@ struct SvcScratch {
     int* mode;            // [m_vec]    0 = ascending order is exact, 1 = replay the hash table
     int* tbl_len;         // [m_vec]    final table length of replayed groups (0 otherwise)
     long long* tbl_off;   // [m_vec+1]  exclusive scan of per-group table scratch
-    long long* totals;    // [2]        {nvec, table scratch ints}
-    int* tables;          // [totals[1]] allocated after the counting pass
+    long long* totals;    // [kSvcTotals] {nvec, scratch ints, groups per replay class (6)}
+    int* tables;          // [totals[1]] replay scratch, allocated after the counting pass
 };
 
-size_t svc_table_ints_per_len(bool with_values);  // scratch ints per unit of tbl_len, as a fraction x4
+constexpr int kSvcTotals = 8;
 
 // Pass 1: per-group distinct counts, mode decision, scans.  Asynchronous on `stream`.
 cudaError_t svc_count_and_scan(const SvcProblem& p, const SvcScratch& s, bool with_values, cudaStream_t stream);
 // Pass 2: emits column lists (and value vectors when out_vals != null; out_vals must be zero-filled).
-cudaError_t svc_emit(const SvcProblem& p, const SvcScratch& s, int* out_col, __half* out_vals, cudaStream_t stream);
+// class_groups = totals[2..8) read back by the host (launches are skipped for empty classes).
+cudaError_t svc_emit(const SvcProblem& p, const SvcScratch& s, const long long* class_groups, int* out_col,
+                     __half* out_vals, cudaStream_t stream);
 
 // Device flag set when a column id outside [0, K) was met (such entries are skipped).
 cudaError_t svc_read_and_clear_bad_column_flag(int* flag, cudaStream_t stream);
