@@ -58,6 +58,26 @@ int sspmm_f16_f16_batched(int m_vec, int vec_length, int N, int K, int batch, co
                           int64_t values_stride, const void* rhs_f16, int64_t rhs_stride, void* out_f16,
                           int64_t out_stride, void* stream);
 
+/*
+ * Same product as sspmm_f16_f16, for callers that must not allocate device memory when they call:
+ * a server that gave all device memory to its own arena at start-up, or a latency-critical loop
+ * in which an allocation could fail or stall other streams.  No counterpart in the reference (its
+ * kernels need no scratch).  Always runs the block kernel; its scratch (a dense transposed copy of
+ * A) lives in a fixed array inside the library image, so
+ *   - K * m_vec * vec_length * 2 must not exceed SSPMM_NOALLOC_MAX_SCRATCH_BYTES, K > 0,
+ *     N % 8 == 0, values / rhs / out 16-byte aligned; anything else is rejected with an error;
+ *   - every GPU that loads the library holds that array until the process exits;
+ *   - all calls on a device share it: two calls whose GPU work overlaps (different streams) race.
+ *     Calls on one stream are safe, and nothing a call leaves in the array is read by the next;
+ *   - the first call on each device looks up the array's device address; make that first call
+ *     before starting any stream capture.
+ * Calls no cudaMalloc / cudaFree / allocating library routine.
+ */
+#define SSPMM_NOALLOC_MAX_SCRATCH_BYTES (8u << 20)
+int sspmm_f16_f16_noalloc(int m_vec, int vec_length, int N, int K, const int* row_indices, const int* row_offsets,
+                          const int* column_indices, const void* values_f16, const void* rhs_f16, void* out_f16,
+                          void* stream);
+
 /* Kernel selection for the calls above: 0 = automatic (default), 1 = tensor-core
  * row-gather kernel only (error if the operands do not qualify), 2 = CUDA-core
  * kernel only, 3 = tensor-core block kernel only.  Process-wide; for tests and profiling. */

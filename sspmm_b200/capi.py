@@ -18,6 +18,7 @@ SIGNATURES = {
     "sspmm_f16_f32": (C.c_int, [C.c_int] * 4 + [_vp] * 7),
     "sspmm_f16_f16": (C.c_int, [C.c_int] * 4 + [_vp] * 7),
     "sspmm_f16_f16_batched": (C.c_int, [C.c_int] * 5 + [_vp, _vp, _vp, _vp, C.c_int64, _vp, C.c_int64, _vp, C.c_int64, _vp]),
+    "sspmm_f16_f16_noalloc": (C.c_int, [C.c_int] * 4 + [_vp] * 7),
     "sspmm_set_kernel": (C.c_int, [C.c_int]),
     "sspmm_device_status": (C.c_int, [c_int_p]),
     "svc_begin": (C.c_int, [C.c_int] * 3 + [_vp, _vp, _vp, _vp, C.POINTER(_vp), C.POINTER(C.c_int64)]),

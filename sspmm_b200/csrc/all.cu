@@ -6,3 +6,4 @@
 #include "svc.cu"
 #include "c_api.cu"
 #include "cxx_api.cu"
+#include "sspmm_noalloc.cu"
