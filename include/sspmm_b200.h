@@ -124,6 +124,20 @@ int svc_replayed_rows(svc_job* job, int64_t* rows);
  */
 int sspmm_sorted_row_swizzle(int m_vec, const int* d_row_offsets, int* d_row_indices, void* stream);
 
+/* ------------------------------------------------------------- .smtx files --- */
+
+/*
+ * The three-line text format between the two stages: "rows, cols, nnz" / row pointers / column
+ * ids.  HOST pointers.  smtx_write replaces CVSE_out, RowMerge/sparse_matrix_format.py:152-175
+ * (byte-identical output); smtx_read_header + smtx_read replace the parsers at
+ * SSpMM/sspmm_test.cpp:28-64 and RowMerge/sparse_matrix_format.py:8-25.  For a compressed file
+ * rows = m_vec and nnz = the ORIGINAL non-zero count (the vector count is row_ptr[m_vec]).
+ */
+int smtx_read_header(const char* path, int* rows, int* cols, int* nnz, int64_t* n_row_ptr, int64_t* n_col_idx);
+int smtx_read(const char* path, int* row_ptr, int64_t n_row_ptr, int* col_idx, int64_t n_col_idx);
+int smtx_write(const char* path, int rows, int cols, int nnz, const int* row_ptr, int64_t n_row_ptr,
+               const int* col_idx, int64_t n_col_idx);
+
 /* ------------------------------------------------------------------ misc --- */
 
 const char* sspmm_last_error_string(void);

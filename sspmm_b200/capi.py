@@ -26,6 +26,9 @@ SIGNATURES = {
     "svc_free": (C.c_int, [_vp]),
     "svc_replayed_rows": (C.c_int, [_vp, C.POINTER(C.c_int64)]),
     "sspmm_sorted_row_swizzle": (C.c_int, [C.c_int, _vp, _vp, _vp]),
+    "smtx_read_header": (C.c_int, [C.c_char_p, c_int_p, c_int_p, c_int_p, C.POINTER(C.c_int64), C.POINTER(C.c_int64)]),
+    "smtx_read": (C.c_int, [C.c_char_p, _vp, C.c_int64, _vp, C.c_int64]),
+    "smtx_write": (C.c_int, [C.c_char_p, C.c_int, C.c_int, C.c_int, _vp, C.c_int64, _vp, C.c_int64]),
     "sspmm_last_error_string": (C.c_char_p, []),
     "sspmm_version": (C.c_char_p, []),
 }

@@ -7,3 +7,4 @@
 #include "c_api.cu"
 #include "cxx_api.cu"
 #include "sspmm_noalloc.cu"
+#include "smtx_io.cu"

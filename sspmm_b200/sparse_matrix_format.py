@@ -23,7 +23,27 @@ from typing import List, Optional, Sequence
 import numpy as np
 import torch
 
-from . import ops
+from . import capi, ops
+
+
+def read_smtx(path):
+    """(rows, cols, nnz, row_ptr int32[], col_idx int32[]) through the library's C++ parser."""
+    import ctypes as C
+    lib = capi.lib()
+    rows, cols, nnz = C.c_int(), C.c_int(), C.c_int()
+    n1, n2 = C.c_int64(), C.c_int64()
+    capi.check(lib.smtx_read_header(os.fsencode(path), C.byref(rows), C.byref(cols), C.byref(nnz), C.byref(n1), C.byref(n2)))
+    row_ptr = np.empty(n1.value, dtype=np.int32)
+    col = np.empty(n2.value, dtype=np.int32)
+    capi.check(lib.smtx_read(os.fsencode(path), row_ptr.ctypes.data, n1.value, col.ctypes.data, n2.value))
+    return rows.value, cols.value, nnz.value, row_ptr, col
+
+
+def write_smtx(path, rows, cols, nnz, row_ptr, col_idx):
+    rp = np.ascontiguousarray(row_ptr, dtype=np.int32)
+    ci = np.ascontiguousarray(col_idx, dtype=np.int32)
+    capi.check(capi.lib().smtx_write(os.fsencode(path), int(rows), int(cols), int(nnz), rp.ctypes.data, rp.size,
+                                     ci.ctypes.data, ci.size))
 
 
 def _device() -> torch.device:
@@ -37,14 +57,7 @@ class sparse_matrix:
     (reference :8-39).  Attributes M, N, nnz, rowPtr, colInd, rowInd."""
 
     def __init__(self, path):
-        with open(path) as f:
-            head = f.readline()
-            row_s = f.readline()
-            col_s = f.readline()
-        M, N, nnz = head.split(", ")
-        self.M, self.N, self.nnz = int(M), int(N), int(nnz)
-        self._row_ptr = np.array(row_s.split(), dtype=np.int64).astype(np.int32)
-        self._col = np.array(col_s.split(), dtype=np.int64).astype(np.int32)
+        self.M, self.N, self.nnz, self._row_ptr, self._col = read_smtx(path)
         self.rowPtr = self._row_ptr.tolist()
         self.colInd = self._col.tolist()
         self.rowInd = np.repeat(np.arange(self.M), np.diff(self._row_ptr[: self.M + 1])).tolist()
@@ -135,11 +148,7 @@ class CVSE:
     def CVSE_out(self, new_dir):
         """"m_vec, K, nnz" / vector row pointers / column ids, space separated, no
         trailing newline (reference :152-175)."""
-        with open(new_dir, "w") as f:
-            f.write(f"{self.num_vec_row}, {self.K}, {self.nnz}\n")
-            f.write(" ".join(map(str, self.vec_row_ptr)))
-            f.write("\n")
-            f.write(" ".join(map(str, self.vec_colInd_list)))
+        write_smtx(new_dir, self.num_vec_row, self.K, self.nnz, self.vec_row_ptr, self.vec_colInd_list)
 
 
 def return_all_zero_vec(vec_len, ROW, COL, origin_matrix):

@@ -15,7 +15,7 @@ HEADER = os.path.join(ROOT, "include", "sspmm_b200.h")
 def declared_functions():
     text = open(HEADER).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b((?:sspmm|svc)_[a-z0-9_]+)\s*\(", text)))
+    return sorted(set(re.findall(r"\b((?:sspmm|svc|smtx)_[a-z0-9_]+)\s*\(", text)))
 
 
 def test_header_declares_the_expected_entry_points():

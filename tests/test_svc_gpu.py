@@ -147,3 +147,31 @@ def test_svc_full_size_properties(lib):
     sub = synthetic.CSR(512, a.K, (a.row_ptr[:513] - a.row_ptr[0]).astype(np.int32), a.col_idx[a.row_ptr[0]:a.row_ptr[512]], a.values[a.row_ptr[0]:a.row_ptr[512]])
     r = svc_oracle.cvse(sub.M, sub.K, sub.nnz, sub.row_lists(), V)
     assert np.array_equal(col[: ptr[64]], np.asarray(r.vec_colInd_list, dtype=np.int32))
+
+
+def test_generate_cvse_file_batch_driver(lib, tmp_path):
+    """The batch entry point row_merge.py calls (reference :190-250): files in, files + CSV rows out."""
+    import csv
+    from sspmm_b200 import sparse_matrix_format as smf
+    names = ["config1_v8", "ffn_512x2048_s98_v8"]
+    src, dest = tmp_path / "dlmc", tmp_path / "dlmc-v8"
+    (src / "sub").mkdir(parents=True)
+    listing = []
+    for n in names:
+        a, _ = CASES[n]
+        rel = f"sub/{n}.smtx"
+        svc_oracle.write_smtx(str(src / rel), a.M, a.K, a.nnz, a.row_ptr.tolist(), a.col_idx.tolist())
+        listing.append(rel)
+    (tmp_path / "paths.txt").write_text("\n".join(listing) + "\n")
+    smf.generate_CVSE_file(str(src) + "/", str(dest) + "/", str(tmp_path / "paths.txt"), 8, csv_dir=str(tmp_path / "csv_data"))
+    rows = list(csv.reader(open(tmp_path / "csv_data" / "RowMerge_V8.csv")))
+    assert len(rows) == len(names)
+    for i, n in enumerate(names):
+        a, V = CASES[n]
+        m, k, nnz, ptr, col = svc_oracle.read_smtx(str(dest / listing[i]))
+        assert (m, k, nnz) == ((a.M + 7) // 8, a.K, a.nnz)
+        assert ptr == GOLD[n + "/vec_row_ptr"].tolist() and col == GOLD[n + "/vec_colInd_list"].tolist()
+        zero = int(GOLD[n + "/all_zero_vec_cnt"][0])
+        exp = [str(i), str(a.M), str(a.K), str(a.nnz), str(svc_oracle.new_sparsity(8, a.M, a.K, a.nnz, zero)), str(zero)] + \
+              [str(x) for x in GOLD[n + "/storage"].tolist()]
+        assert rows[i] == exp
