@@ -383,6 +383,7 @@ def run_ours(args):
         if not args.no_extras:
             extras["svc"] = bench_svc(torch, ops, dev)
             extras["ffn"] = bench_ffn(torch, ops, dev, peaks)
+            extras["encoder_layer"] = bench_encoder(torch, dev)
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
@@ -429,6 +430,24 @@ def bench_svc(torch, ops, dev, ids=(0, 1, 2)):
         nbytes += 4 * (a.M + 1) + 6 * a.nnz + 4 * vp.numel() + 4 * vc.numel() + 2 * vv.numel()
     torch.cuda.synchronize()
     t_dev = time.perf_counter() - t0
+    # the SpMM of the same sweep matrices (B = n x 128)
+    spmm = []
+    for p, c, v, a in dmats:
+        vp, vc, vv, _ = ops.svc(p, c, v, a.M, a.K, 8)
+        B = torch.randn((a.K, 128), device=dev, dtype=torch.float16)
+        C = torch.empty(((vp.numel() - 1) * 8, 128), device=dev, dtype=torch.float16)
+        for _ in range(3):
+            ops.sspmm(vp, vc, vv, B, 8, out=C)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(10):
+            ops.sspmm(vp, vc, vv, B, 8, out=C)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / 10
+        b_alg = 2 * 8 * vc.numel() + 4 * vc.numel() + 4 * vp.numel() + 2 * a.K * 128 + 2 * C.numel()
+        spmm.append({"n": a.M, "us": ms * 1e3, "useful_tflops": 2.0 * a.nnz * 128 / ms / 1e9,
+                     "algorithmic_gbs": b_alg / ms / 1e6, "gather_gbs": 2.0 * vc.numel() * 128 / ms / 1e6})
     t0 = time.perf_counter()
     for a in mats:
         smf.CVSE(a.M, a.K, a.nnz, a.row_lists(), 8)
@@ -440,7 +459,34 @@ def bench_svc(torch, ops, dev, ids=(0, 1, 2)):
     return {"sample": f"sweep matrices {list(ids)} (n = {[a.M for a in mats]}), V=8",
             "device_matrices_per_s": len(mats) / t_dev, "device_gbs": nbytes / t_dev / 1e9,
             "python_entry_point_matrices_per_s": len(mats) / t_host_api,
-            "cpu_oracle_matrices_per_s_1core": len(mats) / t_cpu, "speedup_device_vs_cpu": t_cpu / t_dev}
+            "cpu_oracle_matrices_per_s_1core": len(mats) / t_cpu, "speedup_device_vs_cpu": t_cpu / t_dev,
+            "spmm_n128": spmm}
+
+
+def bench_encoder(torch, dev):
+    """Encoder layer of BASELINE config 4: hidden 768, FFN 3072, 12 heads, seq 512, batch 32, all six weight
+    matrices pruned to 90 % and compressed at V=16; attention and LayerNorm dense."""
+    from sspmm_b200.encoder import SparseEncoderLayer
+    layer = SparseEncoderLayer(hidden=768, ffn=3072, heads=12, sparsity=0.9, vec_length=16, device=dev)
+    batch, seq = 32, 512
+    x = torch.randn(768, batch * seq, device=dev, dtype=torch.float16)
+
+    def t(dense, it=10):
+        for _ in range(3):
+            layer.forward(x, batch, seq, dense=dense)
+        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a0.record()
+        for _ in range(it):
+            layer.forward(x, batch, seq, dense=dense)
+        a1.record()
+        torch.cuda.synchronize()
+        return a0.elapsed_time(a1) / it
+    ms_sparse, ms_dense = t(False), t(True)
+    nnz = sum(l.nnz for l in layer.linears)
+    return {"config": "hidden 768, ffn 3072, 12 heads, seq 512, batch 32, weights 90 % sparse, V=16",
+            "ms_sparse_weights": ms_sparse, "ms_dense_weights_cublas": ms_dense,
+            "linear_useful_tflops": 2.0 * nnz * batch * seq / ms_sparse / 1e9,
+            "note": "whole layer incl. dense attention and LayerNorm; the useful-flop figure counts the six linears only"}
 
 
 def bench_ffn(torch, ops, dev, peaks):
