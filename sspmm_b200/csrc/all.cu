@@ -1,6 +1,7 @@
 // Single translation unit of libsspmm_b200.so: the kernels share file-scope
 // device symbols (status words), which needs one TU without relocatable device code.
 #include "sspmm_gather.cu"
+#include "sspmm_gather_lsu.cu"
 #include "sspmm_simt.cu"
 #include "sspmm_block.cu"
 #include "svc.cu"

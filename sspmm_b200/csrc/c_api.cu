@@ -81,7 +81,7 @@ static long long lookup_nvec(const int* row_offsets, int m_vec, cudaStream_t st)
 static bool block_kernel_is_faster(long long nvec, const SpmmArgs& a) {
     const double n = (double)a.N * a.batch;
     const double mp = (double)a.m_vec * a.V;
-    const double t_gather = 2.0 * (double)nvec * n / 1.7e12 + 6e-6;
+    const double t_gather = 2.0 * (double)nvec * n / 4.0e12 + 6e-6;
     const double t_block = 2.0 * mp * a.K * n / 6.0e14 + 4.0 * mp * a.K / 3e12 + 12e-6;
     return t_block < t_gather;
 }
@@ -153,13 +153,26 @@ static int spmm_entry(int m_vec, int V, int N, int K, int batch, const int* row_
         set_error("block kernel needs 16-byte aligned output, a shared value array for batches and <= 2 GiB of scratch");
         return (int)cudaErrorInvalidValue;
     }
-    bool use_block = choice == 3;
-    if (choice == 0 && block_ok) {
-        const long long nvec = lookup_nvec(row_offsets, m_vec, st);
-        use_block = nvec >= 0 && block_kernel_is_faster(nvec, a);
-    }
-    if (!use_block) {
+    if (choice == 1) {                                     // TMA row-gather producers
         e = launch_sspmm_gather(a);
+        return e == cudaSuccess ? 0 : fail(e, "SpMM launch");
+    }
+    bool use_block = choice == 3;
+    long long nvec = -1;
+    if (choice == 0 || choice == 4) nvec = lookup_nvec(row_offsets, m_vec, st);
+    if (choice == 0 && block_ok) use_block = nvec >= 0 && block_kernel_is_faster(nvec, a);
+    if (!use_block) {                                      // gather kernel with load-instruction producers
+        int chunk = 0, cap = 0;
+        size_t bytes = 0;
+        sspmm_gather_lsu_plan(a, nvec, &chunk, &cap, &bytes);
+        void* scratch = nullptr;
+        if (bytes) {
+            keep_pool_memory();
+            e = cudaMallocAsync(&scratch, bytes, st);
+            if (e != cudaSuccess) return fail(e, "scratch allocation for split rows");
+        }
+        e = launch_sspmm_gather_lsu(a, chunk, cap, scratch);
+        if (scratch) cudaFreeAsync(scratch, st);
         return e == cudaSuccess ? 0 : fail(e, "SpMM launch");
     }
     void* scratch = nullptr;
@@ -210,8 +223,8 @@ int sspmm_f16_f16_batched(int m_vec, int vec_length, int N, int K, int batch, co
 }
 
 int sspmm_set_kernel(int which) {
-    if (which < 0 || which > 3) {
-        set_error("kernel selector must be 0..3");
+    if (which < 0 || which > 4) {
+        set_error("kernel selector must be 0..4");
         return (int)cudaErrorInvalidValue;
     }
     g_kernel_choice.store(which);

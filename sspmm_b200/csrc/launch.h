@@ -30,6 +30,10 @@ struct SpmmArgs {
 
 // tcgen05 row-gather kernel.  Requires N % 8 == 0, 16-byte aligned rhs/values.
 cudaError_t launch_sspmm_gather(const SpmmArgs& a);
+// tcgen05 row-gather kernel with load-instruction producers and splitting of long rows.
+// sspmm_gather_lsu_plan sizes the optional scratch from the vector count (chunk = cap = 0: no splitting).
+void sspmm_gather_lsu_plan(const SpmmArgs& a, long long nvec, int* chunk, int* cap, size_t* scratch_bytes);
+cudaError_t launch_sspmm_gather_lsu(const SpmmArgs& a, int chunk, int cap, void* scratch);
 // tcgen05 block kernel on a dense transposed copy of A held in `scratch`
 // (sspmm_block_scratch_bytes(a) bytes, caller-owned, stream-ordered).
 size_t sspmm_block_scratch_bytes(const SpmmArgs& a);

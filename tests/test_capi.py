@@ -62,6 +62,7 @@ def test_argument_validation_without_gpu(lib):
     assert lib.svc_begin(8, 1 << 30, 8, None, None, None, None, C.byref(job), C.byref(nvec)) == 1
     assert b"exceeds" in lib.sspmm_last_error_string()
     assert lib.sspmm_set_kernel(9) == 1
+    assert lib.sspmm_set_kernel(4) == 0
     assert lib.sspmm_set_kernel(0) == 0
     assert lib.sspmm_version().startswith(b"sspmm_b200")
 

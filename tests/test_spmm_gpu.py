@@ -49,7 +49,7 @@ def gpu_spmm(ptr, col, vals, rhs, V, out_dtype, row_indices=None, kernel=ops.KER
     return out.float().cpu().numpy()
 
 
-@pytest.mark.parametrize("kernel", [ops.KERNEL_GATHER, ops.KERNEL_BLOCK, ops.KERNEL_SIMT])
+@pytest.mark.parametrize("kernel", [ops.KERNEL_GATHER, ops.KERNEL_GATHER_LSU, ops.KERNEL_BLOCK, ops.KERNEL_SIMT])
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.float16])
 @pytest.mark.parametrize("V", [8, 16])
 def test_config1(lib, V, out_dtype, kernel):
@@ -65,7 +65,7 @@ def test_ffn_v16(lib, shape_id, sparsity_id):
     a, rhs = synthetic.ffn(shape_id, sparsity_id)
     ptr, col, vals = compress(a, 16)
     ref = spmm_oracle.sspmm_host(16, ptr, col, vals, rhs, threads=8)
-    for kernel in (ops.KERNEL_GATHER, ops.KERNEL_BLOCK, ops.KERNEL_AUTO):
+    for kernel in (ops.KERNEL_GATHER, ops.KERNEL_GATHER_LSU, ops.KERNEL_BLOCK, ops.KERNEL_AUTO):
         assert_close(gpu_spmm(ptr, col, vals, rhs, 16, torch.float16, kernel=kernel), ref)
         assert_close(gpu_spmm(ptr, col, vals, rhs, 16, torch.float32, kernel=kernel), ref, fp32=True)
 
@@ -88,7 +88,7 @@ def test_ragged_rows_and_column_tails(lib, V, N):
     ptr, col, vals = random_cvse(rng, len(lens), K, V, lens)
     rhs = rng.normal(0, 1, (K, N)).astype(np.float16)
     ref = spmm_oracle.sspmm_host(V, ptr, col, vals, rhs)
-    for kernel in (ops.KERNEL_GATHER, ops.KERNEL_BLOCK):
+    for kernel in (ops.KERNEL_GATHER, ops.KERNEL_GATHER_LSU, ops.KERNEL_BLOCK):
         assert_close(gpu_spmm(ptr, col, vals, rhs, V, torch.float32, kernel=kernel), ref, fp32=True)
         assert_close(gpu_spmm(ptr, col, vals, rhs, V, torch.float16, kernel=kernel), ref)
 
@@ -135,6 +135,21 @@ def test_power_law_sweep_sample(lib):
     rhs = np.random.default_rng(13).normal(0, 1, (a.K, 128)).astype(np.float16)
     ref = spmm_oracle.sspmm_host(8, ptr, col, vals, rhs, threads=8)
     assert_close(gpu_spmm(ptr, col, vals, rhs, 8, torch.float16), ref)
+    assert_close(gpu_spmm(ptr, col, vals, rhs, 8, torch.float32, kernel=ops.KERNEL_GATHER_LSU), ref, fp32=True)
+
+
+def test_long_rows_are_split_and_summed(lib):
+    """A few vector rows far longer than the rest (split into chunks whose partial tiles are summed),
+    next to empty and short rows; N with a partial column tile."""
+    rng = np.random.default_rng(21)
+    K, V, N = 20000, 8, 200
+    lens = [15000, 3, 0, 9000] + [int(x) for x in rng.integers(0, 40, 400)] + [12000]
+    ptr, col, vals = random_cvse(rng, len(lens), K, V, lens)
+    rhs = rng.normal(0, 1, (K, N)).astype(np.float16)
+    ref = spmm_oracle.sspmm_host(V, ptr, col, vals, rhs, threads=8)
+    for dt in (torch.float32, torch.float16):
+        got = gpu_spmm(ptr, col, vals, rhs, V, dt, kernel=ops.KERNEL_GATHER_LSU)
+        assert_close(got, ref, fp32=dt == torch.float32)
 
 
 def test_conv_layer_full_width_properties(lib):
