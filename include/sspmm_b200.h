@@ -115,7 +115,7 @@ int svc_finish(svc_job* job, int* d_vec_row_ptr, int* d_vec_col, void* d_vec_val
 int svc_free(svc_job* job);
 
 /* Number of vector rows whose column order needed the hash-order replay (the
- * others are ascending); diagnostic, valid after svc_begin.  Synchronises. */
+ * others are ascending); diagnostic, valid after svc_begin. */
 int svc_replayed_rows(svc_job* job, int64_t* rows);
 
 /*

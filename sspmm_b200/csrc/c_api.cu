@@ -291,8 +291,7 @@ int svc_begin(int M, int K, int vec_length, const int* d_csr_row_ptr, const int*
     long long totals[kSvcTotals] = {0};
     if (e == cudaSuccess) e = cudaMemcpyAsync(totals, j->s.totals, sizeof totals, cudaMemcpyDeviceToHost, st);
     if (e == cudaSuccess) e = cudaStreamSynchronize(st);
-    int bad = 0;
-    if (e == cudaSuccess) e = svc_read_and_clear_bad_column_flag(&bad, st);
+    const int bad = (int)totals[8];
     if (e != cudaSuccess || bad || totals[0] > 0x7fffffffLL) {
         cudaFreeAsync(base, st);
         delete j;
@@ -342,17 +341,9 @@ int svc_free(svc_job* j) {
 int svc_replayed_rows(svc_job* j, int64_t* rows) {
     g_err[0] = 0;
     if (!j || !rows) return (int)cudaErrorInvalidValue;
-    const size_t mv = (size_t)j->p.m_vec;
     *rows = 0;
-    if (mv == 0) return 0;
-    int* h = new (std::nothrow) int[mv];
-    if (!h) return (int)cudaErrorMemoryAllocation;
-    cudaError_t e = cudaMemcpyAsync(h, j->s.mode, mv * 4, cudaMemcpyDeviceToHost, j->stream);
-    if (e == cudaSuccess) e = cudaStreamSynchronize(j->stream);
-    if (e == cudaSuccess)
-        for (size_t i = 0; i < mv; ++i) *rows += h[i] != 0;
-    delete[] h;
-    return e == cudaSuccess ? 0 : fail(e, "mode read");
+    for (int c = 1; c < 6; ++c) *rows += j->class_groups[c];       // every class but "ascending"
+    return 0;
 }
 
 int sspmm_sorted_row_swizzle(int m_vec, const int* d_row_offsets, int* d_row_indices, void* stream) {

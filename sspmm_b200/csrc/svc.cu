@@ -303,6 +303,8 @@ svc_scan_kernel(int m_vec, int* __restrict__ vec_ptr, const int* __restrict__ tb
         totals[0] = carry_a;
         totals[1] = carry_b;
         for (int c = 0; c < kNumClasses; ++c) totals[2 + c] = hist[c];
+        totals[2 + kNumClasses] = g_svc_bad_column;      // reported with the totals, then cleared
+        g_svc_bad_column = 0;
     }
 }
 

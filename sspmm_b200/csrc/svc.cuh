@@ -28,11 +28,11 @@ struct SvcScratch {
     int* mode;            // [m_vec]    0 = ascending order is exact, 1 = replay the hash table
     int* tbl_len;         // [m_vec]    final table length of replayed groups (0 otherwise)
     long long* tbl_off;   // [m_vec+1]  exclusive scan of per-group table scratch
-    long long* totals;    // [kSvcTotals] {nvec, scratch ints, groups per replay class (6)}
+    long long* totals;    // [kSvcTotals] {nvec, scratch ints, groups per replay class (6), bad-column flag}
     int* tables;          // [totals[1]] replay scratch, allocated after the counting pass
 };
 
-constexpr int kSvcTotals = 8;
+constexpr int kSvcTotals = 9;
 
 // Pass 1: per-group distinct counts, mode decision, scans.  Asynchronous on `stream`.
 cudaError_t svc_count_and_scan(const SvcProblem& p, const SvcScratch& s, bool with_values, cudaStream_t stream);

@@ -97,6 +97,52 @@ def svc(row_ptr: torch.Tensor, col_idx: torch.Tensor, values: Optional[torch.Ten
     return vec_ptr, vec_col, vec_val, replayed.value
 
 
+def svc_batch(mats, vec_length: int):
+    """Sparse vector compression of several independent CSR matrices in one pass.
+
+    ``mats`` is a list of (row_ptr, col_idx, values_or_None, M, K) with device tensors.  Vector rows
+    are independent of one another and their column order does not depend on K, so the matrices are
+    stacked into one tall CSR (each padded with empty rows to a multiple of ``vec_length`` rows, so
+    that no vector row straddles two matrices), compressed once, and the result is cut back into
+    per-matrix pieces.  Returns a list of (vec_row_ptr, vec_col, vec_values_or_None) per matrix and
+    the total number of replayed vector rows.  Throughput path for sweeps of many small matrices."""
+    if not mats:
+        return [], 0
+    V = vec_length
+    dev = mats[0][0].device
+    with_vals = all(m[2] is not None for m in mats)
+    ptr_parts, bases, m_vecs = [], [], []
+    nnz_base, row_base = 0, 0
+    for (rp, ci, va, M, K) in mats:
+        _require(rp, torch.int32, "row_ptr")
+        m_vec = (M + V - 1) // V
+        pad = m_vec * V - M
+        body = rp[:M].to(torch.int64) + nnz_base
+        nnz = int(rp[M].item()) if M > 0 else 0
+        tail = torch.full((pad,), nnz_base + nnz, dtype=torch.int64, device=dev)
+        ptr_parts += [body, tail]
+        bases.append((row_base // V, nnz_base))
+        m_vecs.append(m_vec)
+        nnz_base += nnz
+        row_base += m_vec * V
+    ptr_parts.append(torch.tensor([nnz_base], dtype=torch.int64, device=dev))
+    if nnz_base >= 2 ** 31:
+        raise ValueError("stacked matrix does not fit 32-bit indices")
+    row_ptr = torch.cat(ptr_parts).to(torch.int32)
+    col = torch.cat([m[1][: int(m[0][m[3]].item()) if m[3] > 0 else 0] for m in mats]) if nnz_base else torch.zeros(0, dtype=torch.int32, device=dev)
+    vals = torch.cat([m[2][: int(m[0][m[3]].item()) if m[3] > 0 else 0] for m in mats]) if (with_vals and nnz_base) else (
+        torch.zeros(0, dtype=torch.float16, device=dev) if with_vals else None)
+    K = max(m[4] for m in mats)
+    vec_ptr, vec_col, vec_val, replayed = svc(row_ptr, col.contiguous(), None if vals is None else vals.contiguous(), row_base, K, V)
+    out = []
+    cuts = vec_ptr[torch.tensor([b[0] for b in bases] + [row_base // V], device=dev)].tolist()
+    for k, (vr0, _) in enumerate(bases):
+        lo, hi = cuts[k], cuts[k + 1]
+        p = (vec_ptr[vr0: vr0 + m_vecs[k] + 1] - lo).contiguous()
+        out.append((p, vec_col[lo:hi], None if vec_val is None else vec_val[lo * V: hi * V]))
+    return out, replayed
+
+
 def sorted_row_swizzle(row_offsets: torch.Tensor) -> torch.Tensor:
     _require(row_offsets, torch.int32, "row_offsets")
     m_vec = row_offsets.numel() - 1

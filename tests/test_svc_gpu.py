@@ -175,3 +175,23 @@ def test_generate_cvse_file_batch_driver(lib, tmp_path):
         exp = [str(i), str(a.M), str(a.K), str(a.nnz), str(svc_oracle.new_sparsity(8, a.M, a.K, a.nnz, zero)), str(zero)] + \
               [str(x) for x in GOLD[n + "/storage"].tolist()]
         assert rows[i] == exp
+
+
+def test_svc_batch_equals_one_by_one(lib):
+    """Several matrices of different shapes compressed in one stacked pass give exactly what separate
+    calls give (and therefore what the reference gives)."""
+    dev = torch.device("cuda:0")
+    names = ["ragged_unsorted_v8", "powerlaw_4096_v8", "config1_v8", "ffn_512x2048_s98_v8"]
+    mats = []
+    for n in names:
+        a, _ = CASES[n]
+        mats.append((torch.from_numpy(a.row_ptr).to(dev), torch.from_numpy(a.col_idx).to(dev),
+                     torch.from_numpy(a.values).to(dev), a.M, a.K))
+    res, replayed = ops.svc_batch(mats, 8)
+    assert replayed > 0
+    for n, (p, c, v) in zip(names, res):
+        a, _ = CASES[n]
+        assert np.array_equal(p.cpu().numpy(), GOLD[n + "/vec_row_ptr"])
+        assert np.array_equal(c.cpu().numpy(), GOLD[n + "/vec_colInd_list"])
+        dense = svc_oracle.densify(p.numel() - 1, 8, a.K, p.cpu().tolist(), c.cpu().tolist(), v.cpu().numpy())
+        assert np.array_equal(dense[: a.M].view(np.uint16), a.dense().view(np.uint16))
