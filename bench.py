@@ -524,11 +524,30 @@ def bench_ffn(torch, ops, dev, peaks):
                 a1.record()
                 torch.cuda.synchronize()
                 return a0.elapsed_time(a1) / it
+
+            def t_graph(fn, it=20):
+                """Same call captured `it` times into one CUDA graph: device time per call without host launch cost."""
+                try:
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g):
+                        for _ in range(it):
+                            fn()
+                    g.replay()
+                    torch.cuda.synchronize()
+                    return t(g.replay, it=5) / it
+                except Exception:
+                    torch.cuda.synchronize()
+                    return None
+            Cd = torch.empty((a.M, 256), device=dev, dtype=torch.float16)
             ms = t(lambda: ops.sspmm(vp, vc, vv, B, 16, out=C))
-            ms_d = t(lambda: torch.matmul(A, B))
+            ms_d = t(lambda: torch.matmul(A, B, out=Cd))
+            ms_g = t_graph(lambda: ops.sspmm(vp, vc, vv, B, 16, out=C))
+            ms_dg = t_graph(lambda: torch.matmul(A, B, out=Cd))
             out.append({"shape": list(synthetic.FFN_SHAPES[shape_id]), "sparsity": synthetic.FFN_SPARSITIES[sid],
                         "us": ms * 1e3, "useful_tflops": 2.0 * a.nnz * 256 / ms / 1e9, "cublas_dense_us": ms_d * 1e3,
-                        "cublas_useful_tflops": 2.0 * a.nnz * 256 / ms_d / 1e9, "padding": vc.numel() * 16 / a.nnz})
+                        "cublas_useful_tflops": 2.0 * a.nnz * 256 / ms_d / 1e9, "padding": vc.numel() * 16 / a.nnz,
+                        "us_in_graph": None if ms_g is None else ms_g * 1e3,
+                        "cublas_dense_us_in_graph": None if ms_dg is None else ms_dg * 1e3})
     return {"note": "back-to-back launches, operands L2-resident (problem is ~1-4 MB): latency, not bandwidth",
             "cases": out}
 
