@@ -328,11 +328,28 @@ def run_ours(args):
     h2d = sum(p["K"] * n_loc * 2 for p in probs)
     d2h = sum(p["m_vec"] * p["V"] * n_loc * 2 for p in probs)
 
+    # Three streams: host->device copies, kernels, device->host copies; product p+1's B is on the wire while
+    # product p computes and product p-1's C goes back (every product has its own device buffers).
+    s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+    main = torch.cuda.current_stream()
+
     def e2e_step():
+        s_in.wait_stream(main)
+        s_out.wait_stream(main)
         for p in probs:
-            p["B"].copy_(hostB[p["K"]], non_blocking=True)
+            with torch.cuda.stream(s_in):
+                p["B"].copy_(hostB[p["K"]], non_blocking=True)
+                ev_in = torch.cuda.Event()
+                ev_in.record(s_in)
+            main.wait_event(ev_in)
             launch(p)
-            hostC[p["m_vec"] * p["V"]].copy_(p["C"], non_blocking=True)
+            ev_done = torch.cuda.Event()
+            ev_done.record(main)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_done)
+                hostC[p["m_vec"] * p["V"]].copy_(p["C"], non_blocking=True)
+        main.wait_stream(s_out)
+        main.wait_stream(s_in)
 
     e2e_step()
     barrier()

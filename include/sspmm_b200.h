@@ -125,6 +125,16 @@ int svc_replayed_rows(svc_job* job, int64_t* rows);
  */
 int sspmm_sorted_row_swizzle(int m_vec, const int* d_row_offsets, int* d_row_indices, void* stream);
 
+/*
+ * Row reordering before compression: d_perm[M] = new order of the rows of A (row d_perm[r]
+ * becomes row r), grouping rows that share columns inside windows of 256 rows so that fewer V x 1
+ * vectors are non-zero.  Stands where the reference runs row_merge_reorder.py (README.md:36; data
+ * sets read at SSpMM/sspmm_test.cpp:313-319); that script is absent from the reference checkout, so
+ * this is an extension with its own definition (csrc/reorder.cu), not a bit-exact replacement.
+ */
+int svc_reorder(int M, int K, int vec_length, const int* d_csr_row_ptr, const int* d_csr_col_idx, int* d_perm,
+                void* stream);
+
 /* ------------------------------------------------------------- .smtx files --- */
 
 /*

@@ -24,6 +24,7 @@ SIGNATURES = {
     "svc_begin": (C.c_int, [C.c_int] * 3 + [_vp, _vp, _vp, _vp, C.POINTER(_vp), C.POINTER(C.c_int64)]),
     "svc_finish": (C.c_int, [_vp, _vp, _vp, _vp, _vp]),
     "svc_free": (C.c_int, [_vp]),
+    "svc_reorder": (C.c_int, [C.c_int] * 3 + [_vp] * 4),
     "svc_replayed_rows": (C.c_int, [_vp, C.POINTER(C.c_int64)]),
     "sspmm_sorted_row_swizzle": (C.c_int, [C.c_int, _vp, _vp, _vp]),
     "smtx_read_header": (C.c_int, [C.c_char_p, c_int_p, c_int_p, c_int_p, C.POINTER(C.c_int64), C.POINTER(C.c_int64)]),

@@ -9,3 +9,4 @@
 #include "cxx_api.cu"
 #include "sspmm_noalloc.cu"
 #include "smtx_io.cu"
+#include "reorder.cu"
