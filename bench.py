@@ -17,6 +17,8 @@ host cores, on a bounded sample of the same workload.
 from __future__ import annotations
 
 import argparse
+import contextlib
+import io
 import json
 import os
 import statistics
@@ -580,10 +582,21 @@ def main():
     ap.add_argument("--no-extras", action="store_true", help="skip the SVC and FFN side measurements")
     ap.add_argument("--only", default="", help="layer_id,sparsity_id,V: run a single product (profiling captures)")
     args = ap.parse_args()
-    if args.impl == "reference":
-        run_reference(args)
-    else:
-        run_ours(args)
+    # stdout carries exactly one JSON line: anything libraries print (NCCL banner, ...) goes to stderr
+    sys.stdout.flush()
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
+    out = io.StringIO()
+    with contextlib.redirect_stdout(out):
+        if args.impl == "reference":
+            run_reference(args)
+        else:
+            run_ours(args)
+    sys.stdout.flush()
+    os.dup2(real_stdout, 1)
+    lines = [ln for ln in out.getvalue().splitlines() if ln.startswith("{")]
+    if lines:
+        print(lines[-1], flush=True)
 
 
 if __name__ == "__main__":

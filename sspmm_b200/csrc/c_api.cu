@@ -179,7 +179,7 @@ static int spmm_entry(int m_vec, int V, int N, int K, int batch, const int* row_
     keep_pool_memory();
     e = cudaMallocAsync(&scratch, sspmm_block_scratch_bytes(a), st);
     if (e != cudaSuccess) return fail(e, "scratch allocation for the block kernel");
-    e = launch_sspmm_block(a, scratch);
+    e = launch_sspmm_block(a, scratch, sspmm_block_scratch_bytes(a));
     cudaFreeAsync(scratch, st);
     return e == cudaSuccess ? 0 : fail(e, "SpMM launch");
 }

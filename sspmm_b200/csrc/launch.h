@@ -34,10 +34,11 @@ cudaError_t launch_sspmm_gather(const SpmmArgs& a);
 // sspmm_gather_lsu_plan sizes the optional scratch from the vector count (chunk = cap = 0: no splitting).
 void sspmm_gather_lsu_plan(const SpmmArgs& a, long long nvec, int* chunk, int* cap, size_t* scratch_bytes);
 cudaError_t launch_sspmm_gather_lsu(const SpmmArgs& a, int chunk, int cap, void* scratch);
-// tcgen05 block kernel on a dense transposed copy of A held in `scratch`
-// (sspmm_block_scratch_bytes(a) bytes, caller-owned, stream-ordered).
+// tcgen05 block kernel on a dense transposed copy of A held in `scratch` (caller-owned, stream-ordered).
+// sspmm_block_scratch_bytes(a) is what the kernel would like (copy of A + split-K partial tiles); with less
+// (at least K * m_vec*V halfs) it runs without split-K.
 size_t sspmm_block_scratch_bytes(const SpmmArgs& a);
-cudaError_t launch_sspmm_block(const SpmmArgs& a, void* scratch);
+cudaError_t launch_sspmm_block(const SpmmArgs& a, void* scratch, size_t scratch_bytes);
 // CUDA-core kernel without alignment requirements.
 cudaError_t launch_sspmm_simt(const SpmmArgs& a);
 

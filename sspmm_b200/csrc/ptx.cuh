@@ -83,6 +83,17 @@ __device__ __forceinline__ void tc_fence_after_sync() {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
 
+// ---- programmatic dependent launch -------------------------------------------
+// A kernel launched with the programmatic-stream-serialization attribute may start while the
+// previous kernel of the stream is still running, once every CTA of that kernel has executed
+// griddep_launch_dependents() (or exited).  Until griddep_wait() returns it must touch nothing the
+// previous kernel (or anything before it that was itself launched early) writes; after it, the
+// previous kernel has completed and its writes are visible.
+__device__ __forceinline__ void griddep_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // ---- TMA ------------------------------------------------------------------
 __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");

@@ -45,6 +45,11 @@ __global__ void __launch_bounds__(256)
 expand_transposed_kernel(int m_vec, int K, const int* __restrict__ row_offsets, const int* __restrict__ col,
                          const __half* __restrict__ values, __half* __restrict__ at) {
     __shared__ int slot[kExpandChunk];
+    // Reading the compressed operand (caller input) may overlap the tail of the previous kernel of the
+    // stream; At may still be read by that kernel (the previous product's GEMM), so it is written only
+    // after griddep_wait().  The GEMM of this product may start its prologue right away.
+    griddep_launch_dependents();
+    bool waited = false;
     const int64_t mp = (int64_t)m_vec * V;
     const int k_begin = blockIdx.x * kExpandChunk;
     const int k_end = min(K, k_begin + kExpandChunk);
@@ -57,6 +62,7 @@ expand_transposed_kernel(int m_vec, int K, const int* __restrict__ row_offsets, 
             if (c >= k_begin && c < k_end) slot[c - k_begin] = j;      // duplicates: one of them wins
         }
         __syncthreads();
+        if (!waited) { griddep_wait(); waited = true; }
         for (int k = k_begin + threadIdx.x; k < k_end; k += blockDim.x) {
             const int j = slot[k - k_begin];
             uint4* dst = reinterpret_cast<uint4*>(at + (int64_t)k * mp + (int64_t)i * V);
@@ -71,6 +77,7 @@ expand_transposed_kernel(int m_vec, int K, const int* __restrict__ row_offsets, 
         }
         __syncthreads();
     }
+    if (!waited) griddep_wait();
 }
 
 template <int BN, int STAGES>
@@ -94,6 +101,7 @@ struct BlockLayout {
 struct BlockProblem {
     int Mp, N, K;            // rows of C (m_vec*V), columns, reduction length
     int m_tiles, n_tiles, total_tiles;
+    int splits, steps_per_split;   // split-K: work item z = split, its K steps [z*steps_per_split, ...); 1 = off
     int64_t out_stride;      // per batch, elements
 };
 
@@ -113,6 +121,7 @@ sspmm_block_kernel(const __grid_constant__ CUtensorMap tmap_at, const __grid_con
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kAbortOff);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
+    griddep_launch_dependents();       // the next product's expansion may begin reading its inputs
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(bar_full + 8 * s, 1);
@@ -136,6 +145,7 @@ sspmm_block_kernel(const __grid_constant__ CUtensorMap tmap_at, const __grid_con
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_ptr_smem;
+    griddep_wait();                    // At (and B, C) are touched only from here on
     const int k_steps = (p.K + kBK - 1) / kBK;
     const int tiles_per_batch = p.m_tiles * p.n_tiles;
 
@@ -143,10 +153,13 @@ sspmm_block_kernel(const __grid_constant__ CUtensorMap tmap_at, const __grid_con
         if (lane == 0) {
             uint32_t stage = 0, phase = 0;
             for (int T = blockIdx.x; T < p.total_tiles; T += gridDim.x) {
-                const int b = T / tiles_per_batch, r = T % tiles_per_batch;
+                const int z = T / tiles_per_batch, r = T % tiles_per_batch;
                 const int m0 = (r % p.m_tiles) * kBM, n0 = (r / p.m_tiles) * BN;
+                const int b = p.splits > 1 ? 0 : z;
+                const int ks0 = p.splits > 1 ? z * p.steps_per_split : 0;
+                const int ks1 = p.splits > 1 ? min(k_steps, ks0 + p.steps_per_split) : k_steps;
                 bool ok = true;
-                for (int ks = 0; ks < k_steps; ++ks) {
+                for (int ks = ks0; ks < ks1; ++ks) {
                     if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, kStatusWaitBlock)) { ok = false; break; }
                     const uint32_t full = bar_full + 8 * stage;
                     mbar_arrive_expect_tx(full, L::kAStage + L::kBStage);
@@ -171,7 +184,10 @@ sspmm_block_kernel(const __grid_constant__ CUtensorMap tmap_at, const __grid_con
             if (!mbar_wait(bar_acc_empty + 8 * buf, acc_phase ^ 1u, abort_flag, kStatusWaitBlock)) break;
             tc_fence_after_sync();
             const uint32_t d_tmem = tmem_base + buf * BN;
-            for (int ks = 0; ks < k_steps; ++ks) {
+            const int z = T / tiles_per_batch;
+            const int ks0 = p.splits > 1 ? z * p.steps_per_split : 0;
+            const int ks1 = p.splits > 1 ? min(k_steps, ks0 + p.steps_per_split) : k_steps;
+            for (int ks = ks0; ks < ks1; ++ks) {
                 if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, kStatusWaitBlock)) { ok = false; break; }
                 tc_fence_after_sync();
                 if (lane == 0) {
@@ -183,7 +199,7 @@ sspmm_block_kernel(const __grid_constant__ CUtensorMap tmap_at, const __grid_con
                     for (int kk = 0; kk < nk; ++kk) {
                         const uint64_t a_desc = make_smem_desc(a_s + kk * 2048, L::kChunk, 1024, 2);
                         const uint64_t b_desc = make_smem_desc(b_s + kk * 2048, L::kChunk, 1024, 2);
-                        tc_mma_f16(d_tmem, a_desc, b_desc, idesc, (ks > 0 || kk > 0) ? 1u : 0u);
+                        tc_mma_f16(d_tmem, a_desc, b_desc, idesc, (ks > ks0 || kk > 0) ? 1u : 0u);
                     }
                     tc_commit(bar_empty + 8 * stage);
                 }
@@ -325,18 +341,85 @@ cudaError_t launch_block(const SpmmArgs& a, const CUtensorMap& ta, const CUtenso
         attr_once.mark();
     }
     const int grid = p.total_tiles < sms ? p.total_tiles : sms;
-    kern<<<grid, kBlockThreads, L::kDynamic, a.stream>>>(ta, tb, tc, p);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid); cfg.blockDim = dim3(kBlockThreads); cfg.dynamicSmemBytes = L::kDynamic; cfg.stream = a.stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, p);
+}
+
+// out[i] = sum over splits of partial[s][i], converted once.
+template <typename OutT>
+__global__ void __launch_bounds__(256)
+reduce_splits_kernel(const float* __restrict__ partial, OutT* __restrict__ out, int64_t elems, int splits) {
+    griddep_launch_dependents();
+    griddep_wait();
+    const int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i >= elems) return;                                      // elems is a multiple of 4 (N % 8 == 0)
+    float4 acc = *reinterpret_cast<const float4*>(partial + i);
+    for (int s2 = 1; s2 < splits; ++s2) {
+        const float4 v = *reinterpret_cast<const float4*>(partial + (int64_t)s2 * elems + i);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    if constexpr (sizeof(OutT) == 2) {
+        __half2 lo = __floats2half2_rn(acc.x, acc.y), hi = __floats2half2_rn(acc.z, acc.w);
+        uint2 w;
+        w.x = *reinterpret_cast<uint32_t*>(&lo); w.y = *reinterpret_cast<uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(out + i) = w;
+    } else {
+        *reinterpret_cast<float4*>(out + i) = acc;
+    }
+}
+
+struct BlockPlan {
+    int BN, m_tiles, n_tiles, splits, steps_per_split;
+    size_t at_bytes, partial_bytes;
+};
+
+// Tile shape and split-K factor.  With fewer tiles than SMs every CTA is limited by what one SM can pull
+// from L2, so the K range of a tile is cut into `splits` work items whose fp32 partial tiles are summed by
+// reduce_splits_kernel; `budget` is the scratch the caller can provide.
+BlockPlan plan_block(const SpmmArgs& a, int sms, size_t budget) {
+    BlockPlan pl;
+    const int Mp = a.m_vec * a.V;
+    pl.m_tiles = (Mp + kBM - 1) / kBM;
+    const int64_t tiles256 = (int64_t)pl.m_tiles * ((a.N + 255) / 256) * a.batch;
+    pl.BN = tiles256 >= sms ? 256 : 128;
+    pl.n_tiles = (a.N + pl.BN - 1) / pl.BN;
+    pl.splits = 1;
+    const int k_steps = (a.K + kBK - 1) / kBK;
+    pl.steps_per_split = k_steps;
+    pl.at_bytes = (((size_t)a.K * Mp * sizeof(__half)) + 255) & ~(size_t)255;
+    pl.partial_bytes = 0;
+    const int64_t tiles = (int64_t)pl.m_tiles * pl.n_tiles;
+    if (a.batch == 1 && pl.BN == 128 && tiles * 2 <= sms && k_steps >= 8) {
+        int want = (int)(sms / tiles);
+        if (want > 8) want = 8;
+        if (want > k_steps / 4) want = k_steps / 4;
+        if (want >= 2) {
+            const int sps = (k_steps + want - 1) / want;
+            const int splits = (k_steps + sps - 1) / sps;            // every split gets at least one step
+            const size_t bytes = (size_t)splits * Mp * a.N * sizeof(float);
+            if (splits >= 2 && pl.at_bytes + bytes <= budget) {
+                pl.splits = splits; pl.steps_per_split = sps; pl.partial_bytes = bytes;
+            }
+        }
+    }
+    return pl;
 }
 
 }  // namespace
 
 size_t sspmm_block_scratch_bytes(const SpmmArgs& a) {
-    return (size_t)a.K * (size_t)a.m_vec * a.V * sizeof(__half);
+    const BlockPlan pl = plan_block(a, current_device_sm_count() > 0 ? current_device_sm_count() : 148, ~(size_t)0);
+    return pl.at_bytes + pl.partial_bytes;
 }
 
-// `scratch` holds K * m_vec*V halfs (the transposed dense copy of A), owned by the caller.
-cudaError_t launch_sspmm_block(const SpmmArgs& a, void* scratch) {
+// `scratch` (scratch_bytes long, owned by the caller) holds the transposed dense copy of A
+// (K * m_vec*V halfs) and, when split-K is used, the fp32 partial tiles after it.
+cudaError_t launch_sspmm_block(const SpmmArgs& a, void* scratch, size_t scratch_bytes) {
     EncodeFn enc = block_encode_fn();
     if (!enc) {
         set_error("cuTensorMapEncodeTiled is not available from the CUDA driver");
@@ -352,24 +435,28 @@ cudaError_t launch_sspmm_block(const SpmmArgs& a, void* scratch) {
     {
         const int by = a.m_vec < 32768 ? a.m_vec : 32768;
         const dim3 grid((a.K + kExpandChunk - 1) / kExpandChunk, by);
-        if (a.V == 16)
-            expand_transposed_kernel<16><<<grid, 256, 0, a.stream>>>(a.m_vec, a.K, a.row_offsets, a.column_indices, a.values, at);
-        else
-            expand_transposed_kernel<8><<<grid, 256, 0, a.stream>>>(a.m_vec, a.K, a.row_offsets, a.column_indices, a.values, at);
-        e = cudaGetLastError();
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = grid; cfg.blockDim = dim3(256); cfg.dynamicSmemBytes = 0; cfg.stream = a.stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr; cfg.numAttrs = 1;
+        e = cudaLaunchKernelEx(&cfg, a.V == 16 ? expand_transposed_kernel<16> : expand_transposed_kernel<8>, a.m_vec, a.K,
+                               a.row_offsets, a.column_indices, a.values, at);
         if (e != cudaSuccess) return e;
     }
     const int sms = current_device_sm_count();
     if (sms <= 0) return cudaErrorNoDevice;
-
-    const int m_tiles = (Mp + kBM - 1) / kBM;
-    const int64_t tiles256 = (int64_t)m_tiles * ((a.N + 255) / 256) * a.batch;
-    const bool wide = tiles256 >= sms;          // enough 128x256 tiles to fill the machine
-    const int BN = wide ? 256 : 128;
+    const BlockPlan pl = plan_block(a, sms, scratch_bytes);
+    if (pl.at_bytes > scratch_bytes && (size_t)a.K * Mp * sizeof(__half) > scratch_bytes) {
+        set_error("scratch too small for the block kernel");
+        return cudaErrorInvalidValue;
+    }
     BlockProblem p;
     p.Mp = Mp; p.N = a.N; p.K = a.K;
-    p.m_tiles = m_tiles; p.n_tiles = (a.N + BN - 1) / BN;
-    const int64_t total = (int64_t)p.m_tiles * p.n_tiles * a.batch;
+    p.m_tiles = pl.m_tiles; p.n_tiles = pl.n_tiles;
+    p.splits = pl.splits; p.steps_per_split = pl.steps_per_split;
+    const int64_t total = (int64_t)p.m_tiles * p.n_tiles * (pl.splits > 1 ? pl.splits : a.batch);
     if (total > 0x7fffffffLL) {
         set_error("problem too large for 32-bit tile ids");
         return cudaErrorInvalidValue;
@@ -377,19 +464,34 @@ cudaError_t launch_sspmm_block(const SpmmArgs& a, void* scratch) {
     p.total_tiles = (int)total;
     p.out_stride = a.out_stride;
     CUtensorMap ta, tb, tc;
-    const size_t oes = a.out_f16 ? 2 : 4;
+    const bool split = pl.splits > 1;
+    float* partial = split ? reinterpret_cast<float*>(static_cast<uint8_t*>(scratch) + pl.at_bytes) : nullptr;
+    const bool c_f16 = a.out_f16 && !split;                       // partial tiles are fp32
+    const size_t oes = c_f16 ? 2 : 4;
     if (!encode_2d(enc, &ta, at, (uint64_t)Mp, (uint64_t)a.K, 64, 64) ||
         !encode_3d(enc, &tb, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a.rhs, (uint64_t)a.N, (uint64_t)a.K, (uint64_t)a.batch,
                    (uint64_t)a.rhs_stride, 64, 64, CU_TENSOR_MAP_SWIZZLE_128B) ||
-        !encode_3d(enc, &tc, a.out_f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, oes, a.out,
-                   (uint64_t)a.N, (uint64_t)Mp, (uint64_t)a.batch, (uint64_t)a.out_stride, (uint32_t)(64 / oes), 128,
-                   CU_TENSOR_MAP_SWIZZLE_64B)) {
+        !encode_3d(enc, &tc, c_f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, oes,
+                   split ? static_cast<void*>(partial) : a.out, (uint64_t)a.N, (uint64_t)Mp,
+                   (uint64_t)(split ? pl.splits : a.batch), (uint64_t)(split ? (int64_t)Mp * a.N : a.out_stride),
+                   (uint32_t)(64 / oes), 128, CU_TENSOR_MAP_SWIZZLE_64B)) {
         set_error("cuTensorMapEncodeTiled failed (Mp=%d N=%d K=%d batch=%d)", Mp, a.N, a.K, a.batch);
         return cudaErrorInvalidValue;
     }
-    if (wide)
-        return a.out_f16 ? launch_block<256, 4, __half>(a, ta, tb, tc, p, sms) : launch_block<256, 4, float>(a, ta, tb, tc, p, sms);
-    return a.out_f16 ? launch_block<128, 6, __half>(a, ta, tb, tc, p, sms) : launch_block<128, 6, float>(a, ta, tb, tc, p, sms);
+    if (pl.BN == 256)
+        return c_f16 ? launch_block<256, 4, __half>(a, ta, tb, tc, p, sms) : launch_block<256, 4, float>(a, ta, tb, tc, p, sms);
+    e = c_f16 ? launch_block<128, 6, __half>(a, ta, tb, tc, p, sms) : launch_block<128, 6, float>(a, ta, tb, tc, p, sms);
+    if (e != cudaSuccess || !split) return e;
+    const int64_t elems = (int64_t)Mp * a.N;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)((elems / 4 + 255) / 256)); cfg.blockDim = dim3(256); cfg.stream = a.stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    if (a.out_f16)
+        return cudaLaunchKernelEx(&cfg, reduce_splits_kernel<__half>, (const float*)partial, static_cast<__half*>(a.out), elems, pl.splits);
+    return cudaLaunchKernelEx(&cfg, reduce_splits_kernel<float>, (const float*)partial, static_cast<float*>(a.out), elems, pl.splits);
 }
 
 }  // namespace sspmm_b200

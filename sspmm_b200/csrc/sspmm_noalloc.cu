@@ -88,7 +88,7 @@ extern "C" int sspmm_f16_f16_noalloc(int m_vec, int vec_length, int N, int K, co
     a.stream = static_cast<cudaStream_t>(stream);
     // The expansion kernel writes every element of the K x m_vec*V region it uses (zeros included),
     // so nothing left in the array by an earlier call can leak into this one.
-    e = launch_sspmm_block(a, scratch);
+    e = launch_sspmm_block(a, scratch, kNoAllocScratchBytes);
     if (e != cudaSuccess) {
         set_error("SpMM launch: %s", cudaGetErrorString(e));
         return (int)e;
