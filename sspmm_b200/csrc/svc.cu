@@ -549,103 +549,62 @@ __device__ void replay_group(const SvcProblem& p, int i, int u_final, int cap, i
         if (n_total > u_final) { duplicate = true; break; }     // only possible when the row repeats a column
         PROF_MARK(0)
 
-        // ---- replay  set(list)  for the sequence  D = x[0..n_cur) ++ fresh[0..n_new)
-        // (a) the first 77 elements (tables of 8, 32, 128 slots) by one thread, storing keys
+        // ---- replay  set(list)  for the sequence  D = x[0..n_cur) ++ fresh[0..n_new), level by level.
+        // Inside a level the table length is fixed and insertion is first come, first served: an element
+        // takes a slot with atomicMin on its sequence number; if that displaces a later element, the same
+        // thread carries the displaced element on from the slot it had recorded, so one pass settles all.
         int size = kMinTable, e_len = 0;
         unsigned mask = kMinTable - 1;
-        {
-            int result = 0;                     // bit 31: duplicate met; low bits: table length reached
-            if (tid == 0) {
-                int sz = kMinTable, used = 0;
-                unsigned mk = kMinTable - 1;
-                bool dup = false;
-                for (int s = 0; s < sz; ++s) tab[s] = -1;
-                const int n_seq = min(n_total, kSeqPrefix);
-                for (int t = 0; t < n_seq; ++t) {
-                    const int key = (t < n_cur) ? x[t] : fresh[t - n_cur];
-                    const int sl = find_slot(tab, mk, key);
-                    if (tab[sl] == key) { dup = true; break; }
-                    tab[sl] = key;
-                    ++used;
-                    if (used * 5 >= (int)mk * 3 && sz < 128) {
-                        int cnt = 0;
-                        for (int q = 0; q < sz; ++q) if (tab[q] != -1) seq_other[cnt++] = tab[q];
-                        sz *= 4;
-                        mk = (unsigned)sz - 1u;
-                        for (int q = 0; q < sz; ++q) tab[q] = -1;
-                        for (int q = 0; q < cnt; ++q) tab[find_slot(tab, mk, seq_other[q])] = seq_other[q];
-                    }
-                }
-                result = sz | (dup ? 0x40000000 : 0);
-            }
-            result = Team::max_of(result, red);         // broadcast (other threads hold 0)
-            Team::sync();                               // thread 0's table writes are visible to the team
-            if (result & 0x40000000) { duplicate = true; break; }
-            size = result & 0xffff;
+        for (;;) {
+            long long trig_ll; int next_size;
+            next_level(size, trig_ll, next_size);
+            const int trig = (int)(trig_ll > 0x7fffffff ? 0x7fffffff : trig_ll);
+            const int n_l = min(trig, n_total);
             mask = (unsigned)size - 1u;
-        }
-        PROF_MARK(1)
-        if (n_total >= kSeqPrefix) {
-            // the 77th insertion filled the 128-slot table: it grows to 512 and the team takes over
-            e_len = extract_ordered<Team>(tab, size, nullptr, seq, red);
-            size = 512 > cap ? cap : 512;
-            // (b) remaining levels in parallel: first come, first served with atomicMin on sequence numbers
-            for (;;) {
-                long long trig_ll; int next_size;
-                next_level(size, trig_ll, next_size);
-                const int trig = (int)(trig_ll > 0x7fffffff ? 0x7fffffff : trig_ll);
-                const int n_l = min(trig, n_total);
-                mask = (unsigned)size - 1u;
-                for (int s = tid; s < size; s += Team::kSize) tab[s] = kEmptyPrio;
-                for (int q = e_len + tid; q < n_l; q += Team::kSize) seq[q] = (q < n_cur) ? x[q] : fresh[q - n_cur];
-                Team::sync();
-                for (int q = tid; q < n_l; q += Team::kSize) state[q] = pack_state(probe_begin(seq[q], mask), 0, false);
-                const int first_new = max(e_len, n_cur);
-                PROF_MARK(2)
-                bool dup_here = false;          // also raised when a bound below is hit: the group is then redone sequentially
-                for (int round = 0;; ++round) {
-                    bool changed = false;
-                    if (round > n_l + 16) dup_here = true;
-                    for (int q = tid; q < n_l; q += Team::kSize) {
-                        unsigned st = state[q];
-                        const int key = seq[q];
-                        Probe pr;
-                        unsigned jumps = (st >> 28) & 7u;
+            for (int s = tid; s < size; s += Team::kSize) tab[s] = kEmptyPrio;
+            for (int q = e_len + tid; q < n_l; q += Team::kSize) seq[q] = (q < n_cur) ? x[q] : fresh[q - n_cur];
+            Team::sync();
+            PROF_MARK(2)
+            const int first_new = max(e_len, n_cur);
+            bool dup_here = false;          // also raised when a bound is hit: the group is then redone sequentially
+            volatile unsigned* vstate = state;
+            for (int q = tid; q < n_l && !dup_here; q += Team::kSize) {
+                int e = q;
+                Probe pr = probe_begin(seq[e], mask);
+                unsigned jumps = 0;
+                for (unsigned tries = 0;; ++tries) {
+                    vstate[e] = pack_state(pr, jumps, true);     // where e sits if the next claim succeeds
+                    __threadfence_block();
+                    const int old = atomicMin(&tab[pr.i + pr.w], e);
+                    if (old > e) {
+                        if (old == kEmptyPrio) break;            // free slot taken: this chain ends
+                        // a later element sat here: carry it on from the position it recorded
+                        __threadfence_block();
+                        e = old;
+                        const unsigned st = vstate[e];
+                        jumps = (st >> 28) & 7u;
                         pr.i = st & 0xffffffu; pr.w = (st >> 24) & 15u;
-                        pr.perturb = (jumps >= 7u) ? 0u : ((unsigned)key >> (kPerturbShift * jumps));
-                        bool settled = (st >> 31) != 0;
-                        if (settled) {
-                            if (tab[pr.i + pr.w] == q) continue;
-                            settled = false;                         // displaced by an earlier element: move on
-                            if (probe_advance(pr, mask)) ++jumps;
-                            changed = true;
-                        }
-                        for (unsigned tries = 0;; ++tries) {
-                            const int old = atomicMin(&tab[pr.i + pr.w], q);
-                            if (old > q) { settled = true; changed = true; break; }
-                            if ((q >= first_new && seq[old] == key) || tries > 8u * mask + 64u) { dup_here = true; settled = true; break; }
-                            if (probe_advance(pr, mask)) ++jumps;
-                        }
-                        state[q] = pack_state(pr, jumps, settled);
+                        pr.perturb = (jumps >= 7u) ? 0u : ((unsigned)seq[e] >> (kPerturbShift * jumps));
+                    } else if ((e >= first_new && seq[old] == seq[e]) || tries > 16u * mask + 256u) {
+                        dup_here = true;
+                        break;
                     }
-                    Team::sync();
-                    if (!Team::any(changed && !dup_here, red)) break;
+                    if (probe_advance(pr, mask)) ++jumps;
                 }
-                if (Team::any(dup_here, red)) { duplicate = true; break; }
-                PROF_MARK(3)
-                if (n_total < trig) {
-                    // no further growth: this table is final; keys in place, ordered list out
-                    n_cur = extract_ordered<Team>(tab, size, seq, xn, red);
-                    break;
-                }
-                e_len = extract_ordered<Team>(tab, size, seq, seq_other, red);
-                int* t2 = seq; seq = seq_other; seq_other = t2;
-                size = (next_size > cap) ? cap : next_size;
             }
-            if (duplicate) break;
-        } else {
-            n_cur = extract_ordered<Team>(tab, size, nullptr, xn, red);
+            Team::sync();
+            PROF_MARK(3)
+            if (Team::any(dup_here, red)) { duplicate = true; break; }
+            if (n_total < trig) {
+                // no further growth: this table is final; keys in place, ordered list out
+                n_cur = extract_ordered<Team>(tab, size, seq, xn, red);
+                break;
+            }
+            e_len = extract_ordered<Team>(tab, size, seq, seq_other, red);
+            int* t3 = seq; seq = seq_other; seq_other = t3;
+            size = (next_size > cap) ? cap : next_size;
         }
+        if (duplicate) break;
         int* t2 = x; x = xn; xn = t2;
         mask_prev = mask;
         PROF_MARK(4)
