@@ -219,13 +219,30 @@ def run_ours(args):
     def launch(p):
         ops.sspmm(p["vp"], p["vc"], p["vv"], p["B"], p["V"], out=p["C"])
 
+    # The products of a step are independent of one another, so they are issued round-robin on a few
+    # streams (forked from and joined into the current stream): the tail of one product overlaps the head
+    # of the next, and products with fewer tiles than SMs share the GPU.  With per-launch events
+    # (evs != None) everything stays on the current stream so that each event pair brackets one product.
+    side = [torch.cuda.Stream(device=dev) for _ in range(max(args.streams - 1, 0))]
+
     def step(evs=None):
+        if evs is not None or not side:
+            for i, p in enumerate(probs):
+                if evs is not None:
+                    evs[i][0].record()
+                launch(p)
+                if evs is not None:
+                    evs[i][1].record()
+            return
+        cur = torch.cuda.current_stream()
+        lanes = [cur] + side
+        for st in side:
+            st.wait_stream(cur)
         for i, p in enumerate(probs):
-            if evs is not None:
-                evs[i][0].record()
-            launch(p)
-            if evs is not None:
-                evs[i][1].record()
+            with torch.cuda.stream(lanes[i % len(lanes)]):
+                launch(p)
+        for st in side:
+            cur.wait_stream(st)
 
     for _ in range(max(args.warmup, 3)):
         step()
@@ -390,8 +407,47 @@ def run_ours(args):
             torch.cuda.synchronize()
             dense_ms[key] = a0.elapsed_time(a1) / 5
         dense_total = sum(dense_ms[(p["m_vec"] * p["V"], p["K"])] for p in probs)
+        # the same 32 dense GEMMs issued like our step: round-robin on the same streams, replayed from a CUDA graph
+        dense_A = {}
+        for p in probs:
+            key = (p["m_vec"] * p["V"], p["K"])
+            if key not in dense_A:
+                dense_A[key] = torch.randn(key, device=dev, dtype=torch.float16)
+
+        def dense_step():
+            cur = torch.cuda.current_stream()
+            lanes = [cur] + side
+            for st in side:
+                st.wait_stream(cur)
+            for i, p in enumerate(probs):
+                with torch.cuda.stream(lanes[i % len(lanes)]):
+                    torch.matmul(dense_A[(p["m_vec"] * p["V"], p["K"])], p["B"], out=p["C"])
+            for st in side:
+                cur.wait_stream(st)
+        dense_streams_ms = None
+        try:
+            dense_step()
+            torch.cuda.synchronize()
+            dg = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(dg):
+                dense_step()
+            dg.replay()
+            torch.cuda.synchronize()
+            a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            tot = 0.0
+            for _ in range(5):
+                flush.zero_()
+                a0.record()
+                dg.replay()
+                a1.record()
+                torch.cuda.synchronize()
+                tot += a0.elapsed_time(a1)
+            dense_streams_ms = tot / 5
+        except Exception as exc:  # pragma: no cover
+            sys.stderr.write(f"dense comparator graph failed: {exc}\n")
+            torch.cuda.synchronize()
         extras["comparators"] = {"cublas_dense_fp16": {
-            "ms_per_step": dense_total, "useful_tflops": 2.0 * sum(p["nnz"] for p in probs) * n_loc / dense_total / 1e9,
+            "ms_per_step": dense_total, "ms_per_step_same_streams_graph": dense_streams_ms, "useful_tflops": 2.0 * sum(p["nnz"] for p in probs) * n_loc / dense_total / 1e9,
             "dense_tflops": sum(2.0 * p["m_vec"] * p["V"] * p["K"] * n_loc for p in probs) / dense_total / 1e9,
             "note": "torch.matmul (cuBLAS) on a dense M'xK matrix of the same shape, this rank's columns"}}
         extras["per_product"] = [
@@ -417,7 +473,7 @@ def run_ours(args):
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
                 "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
                 "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-                "config": {"workload": WORKLOAD if not args.only else "single product " + args.only, "N_total": N_total, "N_per_gpu": n_loc, "products_per_step": len(probs), "cuda_graph": graphed,
+                "config": {"workload": WORKLOAD if not args.only else "single product " + args.only, "N_total": N_total, "N_per_gpu": n_loc, "products_per_step": len(probs), "cuda_graph": graphed, "streams": args.streams,
                            "l2": "operands of a step exceed L2 and a 256 MiB buffer is written between steps",
                            "parallelism": f"B and C column-sharded over {world} GPU(s), A_vs replicated, no collective"},
                 "roofline": roof, "cpu_baseline": cpu, "e2e": e2e,
@@ -578,6 +634,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--streams", type=int, default=4, help="streams the independent products of a step are issued on")
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of a CUDA graph of the step")
     ap.add_argument("--no-extras", action="store_true", help="skip the SVC and FFN side measurements")
     ap.add_argument("--only", default="", help="layer_id,sparsity_id,V: run a single product (profiling captures)")
