@@ -139,20 +139,16 @@ def set_order(seq: Iterable[int]) -> List[int]:
 
 def final_table_len(distinct: int) -> int:
     """Table length after adding ``distinct`` different keys to an empty set."""
-    size, used = _MINSIZE, 0
-    thresholds = []
+    size = _MINSIZE
     while True:
         mask = size - 1
-        # smallest fill with 5*fill >= 3*mask
-        trig = -(-3 * mask // 5)
+        trig = -(-3 * mask // 5)            # smallest fill with 5*fill >= 3*mask
         if distinct < trig:
             return size
-        used = trig
-        minused = used * 2 if used > 50000 else used * 4
+        minused = trig * 2 if trig > 50000 else trig * 4
         new = _MINSIZE
         while new <= minused:
             new <<= 1
-        thresholds.append(trig)
         size = new
 
 
