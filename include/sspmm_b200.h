@@ -81,7 +81,8 @@ int sspmm_f16_f16_noalloc(int m_vec, int vec_length, int N, int K, const int* ro
 /* Kernel selection for the calls above: 0 = automatic (default), 1 = tensor-core
  * row-gather kernel fed by TMA gather requests (error if the operands do not qualify),
  * 2 = CUDA-core kernel only, 3 = tensor-core block kernel only, 4 = tensor-core
- * row-gather kernel fed by load instructions.  Process-wide; for tests and profiling. */
+ * row-gather kernel fed by load instructions, 5 = block kernel only and without its
+ * CTA-pair variant (one CTA per tile).  Process-wide; for tests and profiling. */
 int sspmm_set_kernel(int which);
 
 /* Reads (and clears) the device-side status word of the current device:

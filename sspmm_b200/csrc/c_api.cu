@@ -223,11 +223,12 @@ int sspmm_f16_f16_batched(int m_vec, int vec_length, int N, int K, int batch, co
 }
 
 int sspmm_set_kernel(int which) {
-    if (which < 0 || which > 4) {
-        set_error("kernel selector must be 0..4");
+    if (which < 0 || which > 5) {
+        set_error("kernel selector must be 0..5");
         return (int)cudaErrorInvalidValue;
     }
-    g_kernel_choice.store(which);
+    sspmm_block_allow_pairs(which != 5);
+    g_kernel_choice.store(which == 5 ? 3 : which);
     return 0;
 }
 

@@ -39,6 +39,8 @@ cudaError_t launch_sspmm_gather_lsu(const SpmmArgs& a, int chunk, int cap, void*
 // (at least K * m_vec*V halfs) it runs without split-K.
 size_t sspmm_block_scratch_bytes(const SpmmArgs& a);
 cudaError_t launch_sspmm_block(const SpmmArgs& a, void* scratch, size_t scratch_bytes);
+// Allows (default) or forbids the CTA-pair variant of the block kernel.  Process-wide.
+void sspmm_block_allow_pairs(bool allow);
 // CUDA-core kernel without alignment requirements.
 cudaError_t launch_sspmm_simt(const SpmmArgs& a);
 

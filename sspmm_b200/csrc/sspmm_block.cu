@@ -32,6 +32,9 @@ constexpr int kBM = 128;
 constexpr int kBK = 64;
 constexpr int kBlockThreads = 256;
 
+// Process-wide switch for the CTA-pair kernel (tests and profiling compare the two variants).
+std::atomic<bool> g_block_pairs{true};
+
 // ---- expansion of the compressed operand ------------------------------------
 // At[k][i*V .. i*V+V) = values of the vector of row i at column k, or zeros.
 // One CTA per (vector row i, chunk of kExpandChunk columns): the row's column
@@ -290,6 +293,227 @@ sspmm_block_kernel(const __grid_constant__ CUtensorMap tmap_at, const __grid_con
     }
 }
 
+// ---- CTA-pair variant ------------------------------------------------------------
+// Two CTAs (a cluster of two, on neighbouring SMs) share one 256-row x BN-column tile: each holds its
+// own 128 rows of A and HALF of the B tile, and one tcgen05.mma.cta_group::2 (issued by the even CTA)
+// reads both halves, so every SM pulls BN/2 instead of BN columns of B per step from L2 -- the block
+// kernel is limited by what one SM can pull from L2, not by the tensor pipe.  Each CTA's TMEM receives
+// its own 128 rows of D and its own epilogue warps store them.
+//   even CTA   owns the "stage filled" barriers (both CTAs' TMA loads report their bytes there) and
+//              the "accumulator drained" barriers (both CTAs' epilogue warps arrive there)
+//   both CTAs  own a copy of the "stage free" and "accumulator ready" barriers; the MMA thread's
+//              tcgen05.commit arrives on both copies
+template <int BN, int STAGES>
+struct PairLayout {
+    static constexpr int kBH = BN / 2;                           // columns of B held by one CTA
+    static constexpr int kAStage = kBM * kBK * 2;                // 16 KB
+    static constexpr int kBStage = kBH * kBK * 2;                // 16 or 8 KB
+    static constexpr int kChunk = kBK * 128;
+    static constexpr int kAOff = 0;
+    static constexpr int kBOff = STAGES * kAStage;
+    static constexpr int kOutBuf = kBM * 64;
+    static constexpr int kOutOff = kBOff + STAGES * kBStage;
+    static constexpr int kBarOff = kOutOff + 2 * kOutBuf;
+    static constexpr int kNumBars = 2 * STAGES + 4;
+    static constexpr int kTmemPtrOff = kBarOff + kNumBars * 8;
+    static constexpr int kAbortOff = kTmemPtrOff + 8;
+    static constexpr int kBytes = kAbortOff + 8;
+    static constexpr int kDynamic = kBytes + 1024;
+    static constexpr uint32_t kTmemCols = 2 * BN;
+};
+
+template <int BN, int STAGES, typename OutT>
+__global__ void __launch_bounds__(kBlockThreads, 1)
+sspmm_block_pair_kernel(const __grid_constant__ CUtensorMap tmap_at, const __grid_constant__ CUtensorMap tmap_b,
+                        const __grid_constant__ CUtensorMap tmap_c, BlockProblem p) {
+    using L = PairLayout<BN, STAGES>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    const uint32_t sbase = smem_u32(smem);
+    const uint32_t bar_full = sbase + L::kBarOff;
+    const uint32_t bar_empty = bar_full + STAGES * 8;
+    const uint32_t bar_acc_full = bar_empty + STAGES * 8;
+    const uint32_t bar_acc_empty = bar_acc_full + 2 * 8;
+    volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem + L::kTmemPtrOff);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kAbortOff);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_cta_rank();
+    const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+
+    griddep_launch_dependents();
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(bar_full + 8 * s, 1);            // the even CTA's producer; bytes come from both CTAs
+            mbar_init(bar_empty + 8 * s, 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(bar_acc_full + 8 * b, 1);
+            mbar_init(bar_acc_empty + 8 * b, 8);       // four epilogue warps in each CTA
+        }
+        *abort_flag = 0;
+        mbar_fence_init();
+        tma_prefetch_desc(&tmap_at);
+        tma_prefetch_desc(&tmap_b);
+        tma_prefetch_desc(&tmap_c);
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(smem_u32(const_cast<uint32_t*>(tmem_ptr_smem)), L::kTmemCols);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();                // the other CTA's barriers exist before anything is signalled to them
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_ptr_smem;
+    griddep_wait();
+    const int k_steps = (p.K + kBK - 1) / kBK;
+    const int tiles_per_batch = p.m_tiles * p.n_tiles;        // m_tiles counts 256-row pair tiles here
+
+    if (warp == 0) {
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            for (int T = pair; T < p.total_tiles; T += pairs) {
+                const int z = T / tiles_per_batch, r = T % tiles_per_batch;
+                const int m0 = (r % p.m_tiles) * (2 * kBM) + (int)rank * kBM;
+                const int n0 = (r / p.m_tiles) * BN + (int)rank * L::kBH;
+                const int b = p.splits > 1 ? 0 : z;
+                const int ks0 = p.splits > 1 ? z * p.steps_per_split : 0;
+                const int ks1 = p.splits > 1 ? min(k_steps, ks0 + p.steps_per_split) : k_steps;
+                bool ok = true;
+                for (int ks = ks0; ks < ks1; ++ks) {
+                    if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, kStatusWaitBlock)) { ok = false; break; }
+                    if (rank == 0) mbar_arrive_expect_tx(bar_full + 8 * stage, 2 * (L::kAStage + L::kBStage));
+                    const uint32_t full = cluster_map_shared(bar_full + 8 * stage, 0);
+                    const uint32_t a_s = sbase + L::kAOff + stage * L::kAStage;
+                    const uint32_t b_s = sbase + L::kBOff + stage * L::kBStage;
+#pragma unroll
+                    for (int c = 0; c < kBM / 64; ++c)
+                        tma_load_2d_pair(a_s + c * L::kChunk, &tmap_at, m0 + 64 * c, ks * kBK, full);
+#pragma unroll
+                    for (int c = 0; c < L::kBH / 64; ++c)
+                        tma_load_3d_pair(b_s + c * L::kChunk, &tmap_b, n0 + 64 * c, ks * kBK, b, full);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+                if (!ok) break;
+            }
+        }
+    } else if (warp == 1) {
+        if (rank == 0) {
+            constexpr uint32_t idesc = make_idesc_f16_f32(2 * kBM, BN, true, true);
+            uint32_t stage = 0, phase = 0, acc_it = 0;
+            bool ok = true;
+            for (int T = pair; ok && T < p.total_tiles; T += pairs) {
+                const uint32_t buf = acc_it & 1u, acc_phase = (acc_it >> 1) & 1u;
+                if (!mbar_wait(bar_acc_empty + 8 * buf, acc_phase ^ 1u, abort_flag, kStatusWaitBlock)) break;
+                tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                const int z = T / tiles_per_batch;
+                const int ks0 = p.splits > 1 ? z * p.steps_per_split : 0;
+                const int ks1 = p.splits > 1 ? min(k_steps, ks0 + p.steps_per_split) : k_steps;
+                for (int ks = ks0; ks < ks1; ++ks) {
+                    if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, kStatusWaitBlock)) { ok = false; break; }
+                    tc_fence_after_sync();
+                    if (lane == 0) {
+                        const uint32_t a_s = sbase + L::kAOff + stage * L::kAStage;
+                        const uint32_t b_s = sbase + L::kBOff + stage * L::kBStage;
+                        const int rows = min(kBK, p.K - ks * kBK);
+                        const int nk = (rows + 15) >> 4;
+                        for (int kk = 0; kk < nk; ++kk) {
+                            const uint64_t a_desc = make_smem_desc(a_s + kk * 2048, L::kChunk, 1024, 2);
+                            const uint64_t b_desc = make_smem_desc(b_s + kk * 2048, L::kChunk, 1024, 2);
+                            tc_mma_f16_pair(d_tmem, a_desc, b_desc, idesc, (ks > ks0 || kk > 0) ? 1u : 0u);
+                        }
+                        tc_commit_pair(bar_empty + 8 * stage, 3);          // the stage is free in both CTAs
+                    }
+                    __syncwarp();
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+                if (!ok) break;
+                if (lane == 0) tc_commit_pair(bar_acc_full + 8 * buf, 3);  // both CTAs' epilogues may read D
+                __syncwarp();
+                ++acc_it;
+            }
+        }
+    } else if (warp >= 4) {
+        constexpr int kColsPerStore = 64 / (int)sizeof(OutT);
+        constexpr int kStoresPerLoad = 32 / kColsPerStore;
+        const int q = warp & 3;
+        const int row = q * 32 + lane;
+        const bool issuer = (threadIdx.x == 128);
+        const uint32_t swz = (uint32_t)((row >> 1) & 3);
+        uint32_t acc_it = 0, st_it = 0;
+        for (int T = pair; T < p.total_tiles; T += pairs) {
+            const int b = T / tiles_per_batch, r = T % tiles_per_batch;
+            const int m0 = (r % p.m_tiles) * (2 * kBM) + (int)rank * kBM, n0 = (r / p.m_tiles) * BN;
+            const bool rows_exist = m0 < p.Mp;                   // an odd number of 128-row tiles leaves the last half empty
+            const uint32_t buf = acc_it & 1u, acc_phase = (acc_it >> 1) & 1u;
+            if (!named_barrier_and(2, 128, mbar_wait(bar_acc_full + 8 * buf, acc_phase, abort_flag, kStatusWaitBlock))) break;
+            tc_fence_after_sync();
+            const uint32_t drained = cluster_map_shared(bar_acc_empty + 8 * buf, 0);
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN;
+            uint32_t v[2][32];
+            tmem_ld_x32(taddr, v[0]);
+#pragma unroll
+            for (int cc = 0; cc < BN / 32; ++cc) {
+                tc_wait_ld();
+                if (cc + 1 < BN / 32) {
+                    tmem_ld_x32(taddr + (cc + 1) * 32, v[(cc + 1) & 1]);
+                } else {
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(drained);
+                }
+                const uint32_t(&w)[32] = v[cc & 1];
+#pragma unroll
+                for (int h = 0; h < kStoresPerLoad; ++h) {
+                    const uint32_t sb = st_it & 1u;
+                    uint8_t* stage_row = smem + L::kOutOff + sb * L::kOutBuf + row * 64;
+                    named_barrier_sync(1, 128);
+                    if constexpr (sizeof(OutT) == 2) {
+#pragma unroll
+                        for (int g = 0; g < 4; ++g) {
+                            uint4 o;
+                            __half2 h0 = __floats2half2_rn(__uint_as_float(w[g * 8 + 0]), __uint_as_float(w[g * 8 + 1]));
+                            __half2 h1 = __floats2half2_rn(__uint_as_float(w[g * 8 + 2]), __uint_as_float(w[g * 8 + 3]));
+                            __half2 h2 = __floats2half2_rn(__uint_as_float(w[g * 8 + 4]), __uint_as_float(w[g * 8 + 5]));
+                            __half2 h3 = __floats2half2_rn(__uint_as_float(w[g * 8 + 6]), __uint_as_float(w[g * 8 + 7]));
+                            o.x = *reinterpret_cast<uint32_t*>(&h0); o.y = *reinterpret_cast<uint32_t*>(&h1);
+                            o.z = *reinterpret_cast<uint32_t*>(&h2); o.w = *reinterpret_cast<uint32_t*>(&h3);
+                            *reinterpret_cast<uint4*>(stage_row + (((uint32_t)g ^ swz) << 4)) = o;
+                        }
+                    } else {
+#pragma unroll
+                        for (int g = 0; g < 4; ++g) {
+                            const int e = h * 16 + g * 4;
+                            *reinterpret_cast<uint4*>(stage_row + (((uint32_t)g ^ swz) << 4)) =
+                                make_uint4(w[e], w[e + 1], w[e + 2], w[e + 3]);
+                        }
+                    }
+                    fence_proxy_async_smem();
+                    named_barrier_sync(1, 128);
+                    if (issuer) {
+                        if (rows_exist) {
+                            tma_store_3d(&tmap_c, sbase + L::kOutOff + sb * L::kOutBuf, n0 + cc * 32 + h * kColsPerStore, m0, b);
+                            tma_store_commit();
+                        }
+                        tma_store_wait_read<1>();
+                    }
+                    ++st_it;
+                }
+            }
+            ++acc_it;
+        }
+        if (issuer) tma_store_wait_all<0>();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();                // neither CTA leaves while the other may still signal it or read its memory
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc_pair(tmem_base, L::kTmemCols);
+    }
+}
+
 using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -350,6 +574,46 @@ cudaError_t launch_block(const SpmmArgs& a, const CUtensorMap& ta, const CUtenso
     return cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, p);
 }
 
+// Launch of the CTA-pair kernel: clusters of two CTAs; the persistent grid holds as many pairs as the
+// device can keep resident (asked from the occupancy calculator once per device and instantiation).
+template <int BN, int STAGES, typename OutT>
+cudaError_t launch_block_pair(const SpmmArgs& a, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
+                              const BlockProblem& p, int sms) {
+    using L = PairLayout<BN, STAGES>;
+    auto kern = sspmm_block_pair_kernel<BN, STAGES, OutT>;
+    static DeviceOnce attr_once;
+    static std::atomic<int> resident_pairs[64];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaLaunchConfig_t cfg = {};
+    cfg.blockDim = dim3(kBlockThreads); cfg.dynamicSmemBytes = L::kDynamic; cfg.stream = a.stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    if (!attr_once.done()) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
+        if (e != cudaSuccess) return e;
+        cfg.gridDim = dim3(2 * (sms / 2)); cfg.numAttrs = 1;
+        int n = 0;
+        e = cudaOccupancyMaxActiveClusters(&n, kern, &cfg);
+        if (e != cudaSuccess) return e;
+        if (n <= 0) {
+            set_error("no CTA pair of the block kernel fits on this device");
+            return cudaErrorLaunchOutOfResources;
+        }
+        if (dev >= 0 && dev < 64) resident_pairs[dev].store(n, std::memory_order_release);
+        attr_once.mark();
+    }
+    int cap = (dev >= 0 && dev < 64) ? resident_pairs[dev].load(std::memory_order_acquire) : 0;
+    if (cap <= 0 || cap > sms / 2) cap = sms / 2;
+    const int pairs = p.total_tiles < cap ? p.total_tiles : cap;
+    cfg.gridDim = dim3(2 * pairs); cfg.numAttrs = 2;
+    return cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, p);
+}
+
 // out[i] = sum over splits of partial[s][i], converted once.
 template <typename OutT>
 __global__ void __launch_bounds__(256)
@@ -374,19 +638,31 @@ reduce_splits_kernel(const float* __restrict__ partial, OutT* __restrict__ out, 
 }
 
 struct BlockPlan {
+    bool pair;               // CTA-pair kernel: m_tiles counts 256-row tiles
     int BN, m_tiles, n_tiles, splits, steps_per_split;
     size_t at_bytes, partial_bytes;
 };
 
-// Tile shape and split-K factor.  With fewer tiles than SMs every CTA is limited by what one SM can pull
-// from L2, so the K range of a tile is cut into `splits` work items whose fp32 partial tiles are summed by
-// reduce_splits_kernel; `budget` is the scratch the caller can provide.
+// Kernel variant, tile shape and split-K factor.  A "unit" is what holds one tile: an SM, or a pair of
+// SMs for the CTA-pair kernel (used when C has at least two 128-row tiles and pairing wastes little).
+// With fewer tiles than units every CTA is limited by what one SM can pull from L2, so the K range of a
+// tile is cut into `splits` work items whose fp32 partial tiles are summed by reduce_splits_kernel;
+// `budget` is the scratch the caller can provide.
 BlockPlan plan_block(const SpmmArgs& a, int sms, size_t budget) {
     BlockPlan pl;
     const int Mp = a.m_vec * a.V;
-    pl.m_tiles = (Mp + kBM - 1) / kBM;
+    const int m128 = (Mp + kBM - 1) / kBM;
+    // The pair kernel pays a cluster launch and two cluster barriers, and both epilogues gate the next
+    // tile; measured on B200 it wins once every pair of SMs has a 256 x 256 tile and the K loop is long
+    // enough (K >= 512 with fp16 output, K >= 2048 with fp32 output).
+    const int m_pairs = (m128 + 1) / 2;
+    const int64_t pair_tiles256 = (int64_t)m_pairs * ((a.N + 255) / 256) * a.batch;
+    pl.pair = g_block_pairs && m128 >= 2 && (m128 % 2 == 0 || m128 >= 9) && pair_tiles256 >= sms / 2 &&
+              a.K >= (a.out_f16 ? 512 : 2048);
+    pl.m_tiles = pl.pair ? m_pairs : m128;
+    const int units = pl.pair ? sms / 2 : sms;
     const int64_t tiles256 = (int64_t)pl.m_tiles * ((a.N + 255) / 256) * a.batch;
-    pl.BN = tiles256 >= sms ? 256 : 128;
+    pl.BN = tiles256 >= units ? 256 : 128;
     pl.n_tiles = (a.N + pl.BN - 1) / pl.BN;
     pl.splits = 1;
     const int k_steps = (a.K + kBK - 1) / kBK;
@@ -394,8 +670,8 @@ BlockPlan plan_block(const SpmmArgs& a, int sms, size_t budget) {
     pl.at_bytes = (((size_t)a.K * Mp * sizeof(__half)) + 255) & ~(size_t)255;
     pl.partial_bytes = 0;
     const int64_t tiles = (int64_t)pl.m_tiles * pl.n_tiles;
-    if (a.batch == 1 && pl.BN == 128 && tiles * 2 <= sms && k_steps >= 8) {
-        int want = (int)(sms / tiles);
+    if (a.batch == 1 && pl.BN == 128 && tiles * 2 <= units && k_steps >= 8) {
+        int want = (int)(units / tiles);
         if (want > 8) want = 8;
         if (want > k_steps / 4) want = k_steps / 4;
         if (want >= 2) {
@@ -411,6 +687,8 @@ BlockPlan plan_block(const SpmmArgs& a, int sms, size_t budget) {
 }
 
 }  // namespace
+
+void sspmm_block_allow_pairs(bool allow) { g_block_pairs.store(allow); }
 
 size_t sspmm_block_scratch_bytes(const SpmmArgs& a) {
     const BlockPlan pl = plan_block(a, current_device_sm_count() > 0 ? current_device_sm_count() : 148, ~(size_t)0);
@@ -478,9 +756,14 @@ cudaError_t launch_sspmm_block(const SpmmArgs& a, void* scratch, size_t scratch_
         set_error("cuTensorMapEncodeTiled failed (Mp=%d N=%d K=%d batch=%d)", Mp, a.N, a.K, a.batch);
         return cudaErrorInvalidValue;
     }
-    if (pl.BN == 256)
-        return c_f16 ? launch_block<256, 4, __half>(a, ta, tb, tc, p, sms) : launch_block<256, 4, float>(a, ta, tb, tc, p, sms);
-    e = c_f16 ? launch_block<128, 6, __half>(a, ta, tb, tc, p, sms) : launch_block<128, 6, float>(a, ta, tb, tc, p, sms);
+    if (pl.pair) {                                                // always 256-column tiles, never split
+        return c_f16 ? launch_block_pair<256, 6, __half>(a, ta, tb, tc, p, sms)
+                     : launch_block_pair<256, 6, float>(a, ta, tb, tc, p, sms);
+    } else {
+        if (pl.BN == 256)
+            return c_f16 ? launch_block<256, 4, __half>(a, ta, tb, tc, p, sms) : launch_block<256, 4, float>(a, ta, tb, tc, p, sms);
+        e = c_f16 ? launch_block<128, 6, __half>(a, ta, tb, tc, p, sms) : launch_block<128, 6, float>(a, ta, tb, tc, p, sms);
+    }
     if (e != cudaSuccess || !split) return e;
     const int64_t elems = (int64_t)Mp * a.N;
     cudaLaunchConfig_t cfg = {};

@@ -8,7 +8,7 @@ import torch
 
 from . import capi
 
-KERNEL_AUTO, KERNEL_GATHER, KERNEL_SIMT, KERNEL_BLOCK, KERNEL_GATHER_LSU = 0, 1, 2, 3, 4
+KERNEL_AUTO, KERNEL_GATHER, KERNEL_SIMT, KERNEL_BLOCK, KERNEL_GATHER_LSU, KERNEL_BLOCK_SINGLE = 0, 1, 2, 3, 4, 5
 
 
 def _stream_ptr() -> int:

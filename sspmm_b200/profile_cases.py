@@ -4,6 +4,8 @@ where bandwidth matters).
     python -m sspmm_b200.profile_cases gather_powerlaw      # gather SpMM, power-law n=65536, N=1024
     python -m sspmm_b200.profile_cases gather_conv          # gather SpMM forced on conv (2048,512) s=0.9 V=16
     python -m sspmm_b200.profile_cases svc_powerlaw         # SVC of a power-law n=65536 matrix
+    python -m sspmm_b200.profile_cases block_conv_shard     # block SpMM, conv (512,4608) s=0.8 V=8 at the
+                                                            # 8-GPU shard width N=3136 (L2 flushed between launches)
 """
 from __future__ import annotations
 
@@ -37,6 +39,18 @@ def main(case: str) -> None:
         out = torch.empty((vp.numel() - 1) * V, N, device="cuda:0", dtype=torch.float16)
         ops.set_kernel(ops.KERNEL_GATHER_LSU)
         for _ in range(4):
+            ops.sspmm(vp, vc, vv, rhs, V, out=out)
+        ops.set_kernel(ops.KERNEL_AUTO)
+    elif case == "block_conv_shard":
+        a, V, N = synthetic.conv_weight(3, 0), 8, synthetic.CONV_N // 8
+        p, c, v = _dev(a)
+        vp, vc, vv, _ = ops.svc(p, c, v, a.M, a.K, V)
+        rhs = torch.randn(a.K, N, device="cuda:0", dtype=torch.float16)
+        out = torch.empty((vp.numel() - 1) * V, N, device="cuda:0", dtype=torch.float16)
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda:0")
+        ops.set_kernel(ops.KERNEL_BLOCK)
+        for _ in range(4):
+            flush.zero_()
             ops.sspmm(vp, vc, vv, rhs, V, out=out)
         ops.set_kernel(ops.KERNEL_AUTO)
     else:
