@@ -18,6 +18,7 @@ from __future__ import annotations
 
 import argparse
 import contextlib
+import faulthandler
 import io
 import json
 import os
@@ -224,6 +225,8 @@ def run_ours(args):
     # of the next, and products with fewer tiles than SMs share the GPU.  With per-launch events
     # (evs != None) everything stays on the current stream so that each event pair brackets one product.
     side = [torch.cuda.Stream(device=dev) for _ in range(max(args.streams - 1, 0))]
+    # longest product first, so that the short ones fill the gaps at the end of the step
+    issue_order = sorted(range(len(probs)), key=lambda j: -(probs[j]["m_vec"] * probs[j]["V"] * probs[j]["K"]))
 
     def step(evs=None):
         if evs is not None or not side:
@@ -238,9 +241,9 @@ def run_ours(args):
         lanes = [cur] + side
         for st in side:
             st.wait_stream(cur)
-        for i, p in enumerate(probs):
+        for i, j in enumerate(issue_order):
             with torch.cuda.stream(lanes[i % len(lanes)]):
-                launch(p)
+                launch(probs[j])
         for st in side:
             cur.wait_stream(st)
 
@@ -639,6 +642,8 @@ def main():
     ap.add_argument("--no-extras", action="store_true", help="skip the SVC and FFN side measurements")
     ap.add_argument("--only", default="", help="layer_id,sparsity_id,V: run a single product (profiling captures)")
     args = ap.parse_args()
+    # a run that stalls ends with a traceback on stderr instead of holding the GPU until it is killed
+    faulthandler.dump_traceback_later(1500, exit=True)
     # stdout carries exactly one JSON line: anything libraries print (NCCL banner, ...) goes to stderr
     sys.stdout.flush()
     real_stdout = os.dup(1)

@@ -78,11 +78,21 @@ static long long lookup_nvec(const int* row_offsets, int m_vec, cudaStream_t st)
 }
 
 // Modelled times (seconds) of the two tensor-core kernels; constants from measurements on B200.
+// Gather kernel: one work item per (vector row, 128 output columns); an item costs about 1 us plus
+// 0.9 us per 64 gathered rows while items are few (latency of the gather chain), and the whole kernel
+// never beats 4 TB/s of gathered bytes.  Block kernel: expansion + dense GEMM, about 9 us of fixed cost
+// (two or three dependent launches).
 static bool block_kernel_is_faster(long long nvec, const SpmmArgs& a) {
     const double n = (double)a.N * a.batch;
     const double mp = (double)a.m_vec * a.V;
-    const double t_gather = 2.0 * (double)nvec * n / 4.0e12 + 6e-6;
-    const double t_block = 2.0 * mp * a.K * n / 6.0e14 + 4.0 * mp * a.K / 3e12 + 12e-6;
+    const int sms = current_device_sm_count() > 0 ? current_device_sm_count() : 148;
+    const double items = (double)a.m_vec * ((a.N + 127) / 128) * a.batch;
+    const double waves = (items + sms - 1) / sms >= 1.0 ? (double)(long long)((items + sms - 1) / sms) : 1.0;
+    const double steps = (double)nvec / (a.m_vec > 0 ? a.m_vec : 1) / 64.0;
+    const double t_chain = waves * (1.0e-6 + steps * 0.9e-6);
+    const double t_stream = 2.0 * (double)nvec * n / 4.0e12;
+    const double t_gather = 3e-6 + (t_chain > t_stream ? t_chain : t_stream);
+    const double t_block = 2.0 * mp * a.K * n / 6.0e14 + 4.0 * mp * a.K / 3e12 + 9e-6;
     return t_block < t_gather;
 }
 

@@ -60,22 +60,36 @@ expand_transposed_kernel(int m_vec, int K, const int* __restrict__ row_offsets, 
         for (int k = threadIdx.x; k < kExpandChunk; k += blockDim.x) slot[k] = -1;
         __syncthreads();
         const int j0 = row_offsets[i], j1 = row_offsets[i + 1];
-        for (int j = j0 + threadIdx.x; j < j1; j += blockDim.x) {
-            const int c = col[j];
-            if (c >= k_begin && c < k_end) slot[c - k_begin] = j;      // duplicates: one of them wins
+        // four independent loads in flight per thread: the kernel is a chain of dependent reads otherwise
+        for (int j = j0 + threadIdx.x; j < j1; j += 4 * blockDim.x) {
+            int c[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) c[q] = (j + q * (int)blockDim.x < j1) ? __ldg(col + j + q * blockDim.x) : -1;
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+                if (c[q] >= k_begin && c[q] < k_end) slot[c[q] - k_begin] = j + q * blockDim.x;   // duplicates: one of them wins
         }
         __syncthreads();
         if (!waited) { griddep_wait(); waited = true; }
-        for (int k = k_begin + threadIdx.x; k < k_end; k += blockDim.x) {
-            const int j = slot[k - k_begin];
-            uint4* dst = reinterpret_cast<uint4*>(at + (int64_t)k * mp + (int64_t)i * V);
-            if (j >= 0) {
-                const uint4* src = reinterpret_cast<const uint4*>(values + (int64_t)j * V);
+        for (int k = k_begin + threadIdx.x; k < k_end; k += 4 * blockDim.x) {
+            int js[4];
+            uint4 v[4][V / 8];
 #pragma unroll
-                for (int q = 0; q < V / 8; ++q) dst[q] = __ldg(src + q);
-            } else {
+            for (int q = 0; q < 4; ++q) js[q] = (k + q * (int)blockDim.x < k_end) ? slot[k + q * blockDim.x - k_begin] : -1;
 #pragma unroll
-                for (int q = 0; q < V / 8; ++q) dst[q] = make_uint4(0, 0, 0, 0);
+            for (int q = 0; q < 4; ++q) {
+                const uint4* src = reinterpret_cast<const uint4*>(values + (int64_t)(js[q] >= 0 ? js[q] : 0) * V);
+#pragma unroll
+                for (int h = 0; h < V / 8; ++h) v[q][h] = js[q] >= 0 ? __ldg(src + h) : make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const int kq = k + q * (int)blockDim.x;
+                if (kq < k_end) {
+                    uint4* dst = reinterpret_cast<uint4*>(at + (int64_t)kq * mp + (int64_t)i * V);
+#pragma unroll
+                    for (int h = 0; h < V / 8; ++h) dst[h] = v[q][h];
+                }
             }
         }
         __syncthreads();
@@ -669,17 +683,28 @@ BlockPlan plan_block(const SpmmArgs& a, int sms, size_t budget) {
     pl.steps_per_split = k_steps;
     pl.at_bytes = (((size_t)a.K * Mp * sizeof(__half)) + 255) & ~(size_t)255;
     pl.partial_bytes = 0;
-    const int64_t tiles = (int64_t)pl.m_tiles * pl.n_tiles;
-    if (a.batch == 1 && pl.BN == 128 && tiles * 2 <= units && k_steps >= 8) {
-        int want = (int)(units / tiles);
-        if (want > 8) want = 8;
-        if (want > k_steps / 4) want = k_steps / 4;
-        if (want >= 2) {
+    if (pl.pair || a.batch != 1 || tiles256 >= units || k_steps < 8) return pl;
+    // Fewer 256-column tiles than SMs: pick tile width and split-K factor by a small time model
+    // (microseconds, constants measured on B200): a work item costs 2 + steps * 0.40 (128 columns) or
+    // 2 + steps * 0.45 (256 columns); items run in waves of one per SM; summing fp32 partial tiles costs
+    // 3 + their bytes at 4 TB/s.
+    double best = 1e30;
+    for (int bn = 128; bn <= 256; bn += 128) {
+        const int n_tiles = (a.N + bn - 1) / bn;
+        const int64_t tiles = (int64_t)pl.m_tiles * n_tiles;
+        for (int want = 1; want <= 8; ++want) {
             const int sps = (k_steps + want - 1) / want;
-            const int splits = (k_steps + sps - 1) / sps;            // every split gets at least one step
-            const size_t bytes = (size_t)splits * Mp * a.N * sizeof(float);
-            if (splits >= 2 && pl.at_bytes + bytes <= budget) {
-                pl.splits = splits; pl.steps_per_split = sps; pl.partial_bytes = bytes;
+            if (want > 1 && sps < 4) break;
+            const int splits = (k_steps + sps - 1) / sps;                // every split gets at least one step
+            if (splits != want) continue;
+            const size_t bytes = splits > 1 ? (size_t)splits * Mp * a.N * sizeof(float) : 0;
+            if (pl.at_bytes + bytes > budget) continue;
+            const int64_t waves = (tiles * splits + units - 1) / units;
+            double t = (double)waves * (2.0 + sps * (bn == 256 ? 0.45 : 0.40));
+            if (splits > 1) t += 3.0 + ((double)bytes + (double)Mp * a.N * 2.0) / 4.0e6;
+            if (t < best) {
+                best = t;
+                pl.BN = bn; pl.n_tiles = n_tiles; pl.splits = splits; pl.steps_per_split = sps; pl.partial_bytes = bytes;
             }
         }
     }
@@ -759,9 +784,9 @@ cudaError_t launch_sspmm_block(const SpmmArgs& a, void* scratch, size_t scratch_
     if (pl.pair) {                                                // always 256-column tiles, never split
         return c_f16 ? launch_block_pair<256, 6, __half>(a, ta, tb, tc, p, sms)
                      : launch_block_pair<256, 6, float>(a, ta, tb, tc, p, sms);
+    } else if (pl.BN == 256) {
+        e = c_f16 ? launch_block<256, 4, __half>(a, ta, tb, tc, p, sms) : launch_block<256, 4, float>(a, ta, tb, tc, p, sms);
     } else {
-        if (pl.BN == 256)
-            return c_f16 ? launch_block<256, 4, __half>(a, ta, tb, tc, p, sms) : launch_block<256, 4, float>(a, ta, tb, tc, p, sms);
         e = c_f16 ? launch_block<128, 6, __half>(a, ta, tb, tc, p, sms) : launch_block<128, 6, float>(a, ta, tb, tc, p, sms);
     }
     if (e != cudaSuccess || !split) return e;
