@@ -225,8 +225,7 @@ def run_ours(args):
     # of the next, and products with fewer tiles than SMs share the GPU.  With per-launch events
     # (evs != None) everything stays on the current stream so that each event pair brackets one product.
     side = [torch.cuda.Stream(device=dev) for _ in range(max(args.streams - 1, 0))]
-    # longest product first, so that the short ones fill the gaps at the end of the step
-    issue_order = sorted(range(len(probs)), key=lambda j: -(probs[j]["m_vec"] * probs[j]["V"] * probs[j]["K"]))
+    issue_order = list(range(len(probs)))
 
     def step(evs=None):
         if evs is not None or not side:
@@ -637,7 +636,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--streams", type=int, default=4, help="streams the independent products of a step are issued on")
+    ap.add_argument("--streams", type=int, default=8, help="streams the independent products of a step are issued on")
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of a CUDA graph of the step")
     ap.add_argument("--no-extras", action="store_true", help="skip the SVC and FFN side measurements")
     ap.add_argument("--only", default="", help="layer_id,sparsity_id,V: run a single product (profiling captures)")

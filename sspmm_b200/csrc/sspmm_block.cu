@@ -19,6 +19,7 @@
 //   epilogue    tcgen05.ld 32 columns at a time -> fp16/fp32 -> 64-byte rows in a swizzled
 //               staging tile -> TMA store (clips the M and N tails, keeps stores off the LSU)
 #include <cuda.h>
+#include <stdlib.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
@@ -33,7 +34,13 @@ constexpr int kBK = 64;
 constexpr int kBlockThreads = 256;
 
 // Process-wide switch for the CTA-pair kernel (tests and profiling compare the two variants).
-std::atomic<bool> g_block_pairs{true};
+// Programmatic dependent launch between expansion, GEMM and reduction is OFF unless SSPMM_BLOCK_PDL=1:
+// it saves about 1 us per product when products run one after another on one stream, nothing when
+// independent products run on several streams, and with eight streams of such chains in one CUDA graph
+// replays stopped making progress on B200 (dependents that were launched early sit on SMs and wait).
+// Without the launch attribute the griddepcontrol instructions in the kernels do nothing.
+const int g_block_pdl = (getenv("SSPMM_BLOCK_PDL") != nullptr && getenv("SSPMM_BLOCK_PDL")[0] == '1') ? 1 : 0;
+std::atomic<bool> g_block_pairs{getenv("SSPMM_BLOCK_PAIRS") == nullptr || getenv("SSPMM_BLOCK_PAIRS")[0] != '0'};
 
 // ---- expansion of the compressed operand ------------------------------------
 // At[k][i*V .. i*V+V) = values of the vector of row i at column k, or zeros.
@@ -70,7 +77,6 @@ expand_transposed_kernel(int m_vec, int K, const int* __restrict__ row_offsets, 
                 if (c[q] >= k_begin && c[q] < k_end) slot[c[q] - k_begin] = j + q * blockDim.x;   // duplicates: one of them wins
         }
         __syncthreads();
-        if (!waited) { griddep_wait(); waited = true; }
         for (int k = k_begin + threadIdx.x; k < k_end; k += 4 * blockDim.x) {
             int js[4];
             uint4 v[4][V / 8];
@@ -82,6 +88,7 @@ expand_transposed_kernel(int m_vec, int K, const int* __restrict__ row_offsets, 
 #pragma unroll
                 for (int h = 0; h < V / 8; ++h) v[q][h] = js[q] >= 0 ? __ldg(src + h) : make_uint4(0, 0, 0, 0);
             }
+            if (!waited) { griddep_wait(); waited = true; }      // values are in registers: only the stores wait
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
                 const int kq = k + q * (int)blockDim.x;
@@ -584,7 +591,7 @@ cudaError_t launch_block(const SpmmArgs& a, const CUtensorMap& ta, const CUtenso
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr; cfg.numAttrs = 1;
+    cfg.attrs = attr; cfg.numAttrs = g_block_pdl;
     return cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, p);
 }
 
@@ -624,7 +631,7 @@ cudaError_t launch_block_pair(const SpmmArgs& a, const CUtensorMap& ta, const CU
     int cap = (dev >= 0 && dev < 64) ? resident_pairs[dev].load(std::memory_order_acquire) : 0;
     if (cap <= 0 || cap > sms / 2) cap = sms / 2;
     const int pairs = p.total_tiles < cap ? p.total_tiles : cap;
-    cfg.gridDim = dim3(2 * pairs); cfg.numAttrs = 2;
+    cfg.gridDim = dim3(2 * pairs); cfg.numAttrs = 1 + g_block_pdl;
     return cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, p);
 }
 
@@ -743,7 +750,7 @@ cudaError_t launch_sspmm_block(const SpmmArgs& a, void* scratch, size_t scratch_
         cudaLaunchAttribute attr[1];
         attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[0].val.programmaticStreamSerializationAllowed = 1;
-        cfg.attrs = attr; cfg.numAttrs = 1;
+        cfg.attrs = attr; cfg.numAttrs = g_block_pdl;
         e = cudaLaunchKernelEx(&cfg, a.V == 16 ? expand_transposed_kernel<16> : expand_transposed_kernel<8>, a.m_vec, a.K,
                                a.row_offsets, a.column_indices, a.values, at);
         if (e != cudaSuccess) return e;
@@ -796,7 +803,7 @@ cudaError_t launch_sspmm_block(const SpmmArgs& a, void* scratch, size_t scratch_
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr; cfg.numAttrs = 1;
+    cfg.attrs = attr; cfg.numAttrs = g_block_pdl;
     if (a.out_f16)
         return cudaLaunchKernelEx(&cfg, reduce_splits_kernel<__half>, (const float*)partial, static_cast<__half*>(a.out), elems, pl.splits);
     return cudaLaunchKernelEx(&cfg, reduce_splits_kernel<float>, (const float*)partial, static_cast<float*>(a.out), elems, pl.splits);
