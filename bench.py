@@ -465,6 +465,11 @@ def run_ours(args):
             extras["ffn"] = bench_ffn(torch, ops, dev, peaks)
             extras["encoder_layer"] = bench_encoder(torch, dev)
 
+    if not args.no_extras and not args.only:
+        sweep = bench_sweep(torch, ops, dev, dist, rank, world)
+        if rank == 0:
+            extras["sweep"] = sweep
+
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu:
         s = cpu_sample()
@@ -551,6 +556,39 @@ def bench_svc(torch, ops, dev, ids=(0, 1, 2, 3, 4, 5, 6, 7)):
             "python_entry_point_matrices_per_s": len(mats) / t_host_api,
             "cpu_oracle_matrices_per_s_1core": len(mats) / t_cpu, "speedup_device_vs_cpu": t_cpu / t_dev,
             "spmm_n128": spmm}
+
+
+def bench_sweep(torch, ops, dev, dist, rank, world, per_rank=8):
+    """The power-law sweep distributed over ranks (matrix_id mod world): every rank compresses its
+    matrices (V=8) and multiplies each by B = n x 128; wall time of the slowest rank, device-resident
+    inputs, no collective on the data path."""
+    ids = [rank + world * k for k in range(per_rank)]
+    mats = [synthetic.sweep_matrix(i) for i in ids]
+    dmats = [(torch.from_numpy(a.row_ptr).to(dev), torch.from_numpy(a.col_idx).to(dev), torch.from_numpy(a.values).to(dev),
+              a, torch.randn((a.K, 128), device=dev, dtype=torch.float16)) for a in mats]
+
+    def one_pass():
+        for p, c, v, a, B in dmats:
+            vp, vc, vv, _ = ops.svc(p, c, v, a.M, a.K, 8)
+            ops.sspmm(vp, vc, vv, B, 8)
+
+    one_pass()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    t0 = time.perf_counter()
+    one_pass()
+    torch.cuda.synchronize()
+    t = torch.tensor([time.perf_counter() - t0], device=dev, dtype=torch.float64)
+    nnz = torch.tensor([float(sum(a.nnz for a in mats))], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.all_reduce(nnz, op=dist.ReduceOp.SUM)
+    sec = float(t.item())
+    return {"matrices": per_rank * world, "matrices_per_rank": per_rank, "seconds_slowest_rank": sec,
+            "svc_plus_spmm_matrices_per_s": per_rank * world / sec,
+            "useful_tflops_n128": 2.0 * float(nnz.item()) * 128 / sec / 1e12,
+            "note": "matrix_id mod world -> rank; SVC (V=8) then SpMM with B = n x 128 per matrix; weak scaling"}
 
 
 def bench_encoder(torch, dev):

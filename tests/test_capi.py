@@ -63,6 +63,8 @@ def test_argument_validation_without_gpu(lib):
     assert b"exceeds" in lib.sspmm_last_error_string()
     assert lib.sspmm_set_kernel(9) == 1
     assert lib.sspmm_set_kernel(4) == 0
+    assert lib.sspmm_set_kernel(5) == 0
+    assert lib.sspmm_set_kernel(6) == 1
     assert lib.sspmm_set_kernel(0) == 0
     assert lib.sspmm_version().startswith(b"sspmm_b200")
 

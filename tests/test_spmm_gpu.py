@@ -173,6 +173,25 @@ def test_conv_layer_full_width_properties(lib):
     assert np.array_equal(got2, 2 * got)
 
 
+@pytest.mark.parametrize("M,K,N", [(512, 1024, 9472),     # two CTA-pair tiles per column tile, every SM pair busy
+                                   (1152, 512, 3840),     # nine 128-row tiles: the last pair has an empty half
+                                   (512, 4608, 3136)])    # fewer wide tiles than SMs: 256-column tiles, split-K
+@pytest.mark.parametrize("out_dtype", [torch.float16, torch.float32])
+def test_block_kernel_variants_agree(lib, M, K, N, out_dtype):
+    """The CTA-pair form, the one-CTA form and the split-K form of the block kernel against each other and,
+    on a sample of vector rows, against the oracle."""
+    rng = np.random.default_rng(M + K + N)
+    a = synthetic.magnitude_pruned(M, K, 0.8, rng)
+    V = 8
+    ptr, col, vals = compress(a, V)
+    rhs = rng.normal(0, 1, (K, N)).astype(np.float16)
+    got = gpu_spmm(ptr, col, vals, rhs, V, out_dtype, kernel=ops.KERNEL_BLOCK)
+    got_single = gpu_spmm(ptr, col, vals, rhs, V, out_dtype, kernel=ops.KERNEL_BLOCK_SINGLE)
+    assert_close(got, got_single, fp32=out_dtype == torch.float32)
+    for rows in ((0, 2), (M // V - 2, M // V)):
+        ref = spmm_oracle.sspmm_host(V, ptr, col, vals, rhs, rows=rows, threads=8)
+        assert_close(got[rows[0] * V: rows[1] * V], ref, fp32=out_dtype == torch.float32)
+
 @pytest.mark.skipif(not ref_kernel.available(), reason="reference kernel library not built")
 @pytest.mark.parametrize("V", [8, 16])
 def test_against_reference_gpu_kernel(lib, V):
