@@ -16,9 +16,12 @@ is no CPU implementation here, and a missing library or GPU is an error."""
 from __future__ import annotations
 
 import csv
+import functools
+import itertools
 import math
 import os
-from typing import List, Optional, Sequence
+from collections.abc import Sequence
+from typing import List, Optional
 
 import numpy as np
 import torch
@@ -58,13 +61,24 @@ class sparse_matrix:
 
     def __init__(self, path):
         self.M, self.N, self.nnz, self._row_ptr, self._col = read_smtx(path)
-        self.rowPtr = self._row_ptr.tolist()
-        self.colInd = self._col.tolist()
-        self.rowInd = np.repeat(np.arange(self.M), np.diff(self._row_ptr[: self.M + 1])).tolist()
+
+    # list attributes of the reference, built on first use
+    @functools.cached_property
+    def rowPtr(self):
+        return self._row_ptr.tolist()
+
+    @functools.cached_property
+    def colInd(self):
+        return self._col.tolist()
+
+    @functools.cached_property
+    def rowInd(self):
+        return np.repeat(np.arange(self.M), np.diff(self._row_ptr[: self.M + 1])).tolist()
 
     def colInd_list_array(self):
-        p, c = self.rowPtr, self.colInd
-        return [c[p[i]:p[i + 1]] for i in range(self.M)]
+        """Per-row column lists (reference :41-53) as a sequence that also carries the CSR arrays, so
+        that CVSE can skip the list -> array conversion."""
+        return _CsrRows(self._row_ptr[: self.M + 1], self._col)
 
     def origin_matrix(self):
         """The reference returns a dense M x N list of 0/1 lists (:55-67) whose only
@@ -90,14 +104,34 @@ class OriginMatrix:
         return row
 
 
+class _CsrRows(Sequence):
+    """Read-only sequence of per-row column lists over CSR arrays; rows are cut on access."""
+
+    def __init__(self, row_ptr, col):
+        self.csr = (row_ptr, col)
+
+    def __len__(self):
+        return len(self.csr[0]) - 1
+
+    def __getitem__(self, i):
+        p, c = self.csr
+        if isinstance(i, slice):
+            return [c[p[k]:p[k + 1]].tolist() for k in range(*i.indices(len(self)))]
+        if i < 0:
+            i += len(self)
+        if not 0 <= i < len(self):
+            raise IndexError(i)
+        return c[p[i]:p[i + 1]].tolist()
+
+    def __eq__(self, other):
+        return len(self) == len(other) and all(a == b for a, b in zip(self, other))
+
+
 def _csr_from_lists(rows: Sequence[Sequence[int]]):
-    lens = np.fromiter((len(r) for r in rows), dtype=np.int64, count=len(rows))
+    lens = np.fromiter(map(len, rows), dtype=np.int64, count=len(rows))
     row_ptr = np.zeros(len(rows) + 1, dtype=np.int64)
     np.cumsum(lens, out=row_ptr[1:])
-    if row_ptr[-1] > 0:
-        col = np.concatenate([np.asarray(r, dtype=np.int64) for r in rows if len(r)])
-    else:
-        col = np.zeros(0, dtype=np.int64)
+    col = np.fromiter(itertools.chain.from_iterable(rows), dtype=np.int64, count=int(row_ptr[-1]))
     if row_ptr[-1] >= 2 ** 31 or (col.size and (col.min() < 0 or col.max() >= 2 ** 31)):
         raise ValueError("matrix does not fit 32-bit indices")
     return row_ptr.astype(np.int32), col.astype(np.int32)
@@ -110,7 +144,11 @@ class CVSE:
     def __init__(self, ROW, COL, NNZ, colInd_list_array, vec_len, values=None):
         self.M, self.K, self.nnz, self.vec_len = ROW, COL, NNZ, vec_len
         self.num_vec_row = math.ceil(ROW / vec_len)
-        row_ptr, col = _csr_from_lists(colInd_list_array[:ROW])
+        csr = getattr(colInd_list_array, "csr", None)
+        if csr is not None and len(colInd_list_array) == ROW:
+            row_ptr, col = np.ascontiguousarray(csr[0], dtype=np.int32), np.ascontiguousarray(csr[1], dtype=np.int32)
+        else:
+            row_ptr, col = _csr_from_lists(colInd_list_array[:ROW])
         dev = _device()
         d_ptr = torch.from_numpy(row_ptr).to(dev)
         d_col = torch.from_numpy(col).to(dev)
@@ -120,17 +158,29 @@ class CVSE:
         vec_ptr, vec_col, vec_val, replayed = ops.svc(d_ptr, d_col, d_val, ROW, COL, vec_len)
         self.replayed_rows = replayed
         self.d_vec_row_ptr, self.d_vec_col, self.d_vec_values = vec_ptr, vec_col, vec_val
-        ptr = vec_ptr.cpu().numpy()
-        cols = vec_col.cpu().numpy()
-        self.vec_row_ptr = ptr.tolist()
-        self.vec_colInd_list = cols.tolist()
-        self.num_vec = int(ptr[-1])
-        lens = np.diff(ptr)
-        self.tile_num = (-(-lens // 32)).tolist()
-        l = self.vec_colInd_list
-        p = self.vec_row_ptr
-        self.vec_colInd_list_array = [l[p[i]:p[i + 1]] for i in range(self.num_vec_row)]
+        self._ptr = vec_ptr.cpu().numpy()
+        self._cols = vec_col.cpu().numpy()
+        self.num_vec = int(self._ptr[-1])
         self.values = None if vec_val is None else vec_val.cpu().numpy()
+
+    # The list attributes of the reference are built on first use: turning a million column ids into
+    # Python ints costs more than the compression itself.
+    @functools.cached_property
+    def vec_row_ptr(self):
+        return self._ptr.tolist()
+
+    @functools.cached_property
+    def vec_colInd_list(self):
+        return self._cols.tolist()
+
+    @functools.cached_property
+    def tile_num(self):
+        return (-(-np.diff(self._ptr) // 32)).tolist()
+
+    @functools.cached_property
+    def vec_colInd_list_array(self):
+        l, p = self.vec_colInd_list, self.vec_row_ptr
+        return [l[p[i]:p[i + 1]] for i in range(self.num_vec_row)]
 
     # storage models (reference :124-150): 4-byte indices, 2-byte values
     def return_CSR_storage(self):
@@ -140,15 +190,18 @@ class CVSE:
         return self.num_vec * self.vec_len * 2 + (self.num_vec_row + 1) * 4 + self.num_vec * 4
 
     def return_TCF_storage(self):
-        return self.nnz * 2 + self.nnz * 3 * 4 + (self.M + 1) * 4 + sum(self.tile_num) * 32 * 4
+        return self.nnz * 2 + self.nnz * 3 * 4 + (self.M + 1) * 4 + self._tiles() * 32 * 4
 
     def return_SRBCSR_storage(self):
-        return self.num_vec * self.vec_len * 2 + (self.num_vec_row + 1) * 4 + sum(self.tile_num) * 32 * 4
+        return self.num_vec * self.vec_len * 2 + (self.num_vec_row + 1) * 4 + self._tiles() * 32 * 4
+
+    def _tiles(self):
+        return int((-(-np.diff(self._ptr) // 32)).sum())
 
     def CVSE_out(self, new_dir):
         """"m_vec, K, nnz" / vector row pointers / column ids, space separated, no
         trailing newline (reference :152-175)."""
-        write_smtx(new_dir, self.num_vec_row, self.K, self.nnz, self.vec_row_ptr, self.vec_colInd_list)
+        write_smtx(new_dir, self.num_vec_row, self.K, self.nnz, self._ptr, self._cols)
 
 
 def return_all_zero_vec(vec_len, ROW, COL, origin_matrix):
@@ -192,8 +245,7 @@ def generate_CVSE_file(src_dir, dest_dir, paths_txt, vec_len, csv_dir="./csv_dat
         for i, name in enumerate(names):
             m0 = sparse_matrix(src_dir + name)
             c = CVSE(m0.M, m0.N, m0.nnz, m0.colInd_list_array(), vec_len)
-            ok = (c.num_vec_row == len(c.vec_colInd_list_array) and c.num_vec_row + 1 == len(c.vec_row_ptr)
-                  and c.num_vec == c.vec_row_ptr[-1] == len(c.vec_colInd_list))
+            ok = c.num_vec_row + 1 == c._ptr.size and c.num_vec == int(c._ptr[-1]) == c._cols.size
             if not ok:
                 print("NO.", i, "  format error")
                 break
