@@ -71,6 +71,7 @@ constexpr int kSCapU = 306, kSCapT = 512;
 constexpr int kM1CapU = 1228, kM1CapT = 2048;
 constexpr int kM2CapU = 4914, kM2CapT = 8192;
 constexpr int kLCapT = 32768;
+constexpr int kLStateInts = 19664;   // a table of kLCapT slots holds fewer than 19661 keys; STATE of class L sits in shared memory
 constexpr int kListsPerGroup = 5;   // X2, NEW, P, Q, STATE (the sixth list is the output slice)
 
 __host__ __device__ inline void next_level(int size, long long& trig, int& next_size) {
@@ -173,6 +174,22 @@ struct BlockTeam {
         for (int w = 1; w < THREADS / 32; ++w) t = max(t, scratch[w]);
         __syncthreads();
         return t;
+    }
+    // exclusive prefix sum of v over the threads of the block, in thread order
+    __device__ static int scan_exclusive(int v, int& total, int* scratch) {
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+        const int inc = warp_incl_scan(v, lane);
+        if (lane == 31) scratch[warp] = inc;
+        __syncthreads();
+        int before = 0, all = 0;
+        for (int w = 0; w < THREADS / 32; ++w) {
+            const int c = scratch[w];
+            if (w < warp) before += c;
+            all += c;
+        }
+        __syncthreads();
+        total = all;
+        return before + inc - v;
     }
     __device__ static int rank(bool flag, int& total, int* scratch) {
         const unsigned b = __ballot_sync(0xffffffffu, flag);
@@ -444,6 +461,53 @@ struct ReplayBuffers {
 template <class Team>
 __device__ int extract_ordered(int* tab, int size, const int* seq, int* dst, int* red) {
     const int tid = Team::tid();
+    if constexpr (Team::kSize >= 256) {
+        // Large table, CTA team: every warp owns a contiguous run of size / warps slots and walks it 32
+        // slots at a time (one ballot gives the occupancy of a row), so the whole table needs one prefix sum
+        // over warp totals instead of a block-wide one per kSize slots, and the key lookups of four rows
+        // are in flight together.
+        if (size >= Team::kSize) {
+            const int lane = tid & 31, warp = tid >> 5;
+            const int rows = size / Team::kSize;                    // rows of 32 slots per warp
+            const int first = warp * rows * 32 + lane;
+            int cnt = 0;
+            for (int j = 0; j < rows; ++j) {
+                const int e = tab[first + j * 32];
+                cnt += __popc(__ballot_sync(0xffffffffu, seq ? (e != kEmptyPrio) : (e != -1)));
+            }
+            if (lane == 0) red[warp] = cnt;
+            Team::sync();
+            int pos = 0, total = 0;
+            for (int w = 0; w < Team::kSize / 32; ++w) {
+                const int c = red[w];
+                if (w < warp) pos += c;
+                total += c;
+            }
+            Team::sync();
+            for (int j0 = 0; j0 < rows; j0 += 4) {
+                int e4[4], k4[4];
+                bool f4[4];
+#pragma unroll
+                for (int b = 0; b < 4; ++b) {
+                    e4[b] = (j0 + b < rows) ? tab[first + (j0 + b) * 32] : (seq ? kEmptyPrio : -1);
+                    f4[b] = seq ? (e4[b] != kEmptyPrio) : (e4[b] != -1);
+                }
+#pragma unroll
+                for (int b = 0; b < 4; ++b) k4[b] = f4[b] ? (seq ? seq[e4[b]] : e4[b]) : -1;
+#pragma unroll
+                for (int b = 0; b < 4; ++b) {
+                    if (j0 + b < rows) {
+                        const unsigned m = __ballot_sync(0xffffffffu, f4[b]);
+                        if (f4[b]) dst[pos + __popc(m & ((1u << lane) - 1u))] = k4[b];
+                        if (seq) tab[first + (j0 + b) * 32] = k4[b];
+                        pos += __popc(m);
+                    }
+                }
+            }
+            Team::sync();
+            return total;
+        }
+    }
     int n = 0;
     for (int s0 = 0; s0 < size; s0 += Team::kSize) {
         const int s = s0 + tid;
@@ -562,15 +626,32 @@ __device__ void replay_group(const SvcProblem& p, int i, int u_final, int cap, i
             const int n_l = min(trig, n_total);
             mask = (unsigned)size - 1u;
             for (int s = tid; s < size; s += Team::kSize) tab[s] = kEmptyPrio;
-            for (int q = e_len + tid; q < n_l; q += Team::kSize) seq[q] = (q < n_cur) ? x[q] : fresh[q - n_cur];
+            for (int q = e_len + tid; q < n_l; q += 4 * Team::kSize) {          // four loads in flight
+                int v4[4];
+#pragma unroll
+                for (int b = 0; b < 4; ++b) {
+                    const int qq = q + b * Team::kSize;
+                    v4[b] = (qq < n_l) ? ((qq < n_cur) ? x[qq] : fresh[qq - n_cur]) : 0;
+                }
+#pragma unroll
+                for (int b = 0; b < 4; ++b)
+                    if (q + b * Team::kSize < n_l) seq[q + b * Team::kSize] = v4[b];
+            }
             Team::sync();
             PROF_MARK(2)
             const int first_new = max(e_len, n_cur);
             bool dup_here = false;          // also raised when a bound is hit: the group is then redone sequentially
             volatile unsigned* vstate = state;
-            for (int q = tid; q < n_l && !dup_here; q += Team::kSize) {
+            for (int q4 = tid; q4 < n_l && !dup_here; q4 += 4 * Team::kSize) {
+              int k4[4];
+#pragma unroll
+              for (int b = 0; b < 4; ++b) k4[b] = (q4 + b * Team::kSize < n_l) ? seq[q4 + b * Team::kSize] : 0;
+#pragma unroll
+              for (int b = 0; b < 4; ++b) {
+                const int q = q4 + b * Team::kSize;
+                if (q >= n_l || dup_here) break;
                 int e = q;
-                Probe pr = probe_begin(seq[e], mask);
+                Probe pr = probe_begin(k4[b], mask);
                 unsigned jumps = 0;
                 for (unsigned tries = 0;; ++tries) {
                     vstate[e] = pack_state(pr, jumps, true);     // where e sits if the next claim succeeds
@@ -591,6 +672,7 @@ __device__ void replay_group(const SvcProblem& p, int i, int u_final, int cap, i
                     }
                     if (probe_advance(pr, mask)) ++jumps;
                 }
+              }
             }
             Team::sync();
             PROF_MARK(3)
@@ -677,6 +759,7 @@ svc_emit_replay_kernel(SvcProblem p, const int* __restrict__ vec_ptr, const int*
             int* g = scratch + tbl_off[i];
             for (int l = 0; l < kListsPerGroup; ++l) b.lists[l] = g + (size_t)l * u;
             b.table = (CLASS == kClassL) ? mine : g + (size_t)kListsPerGroup * u;
+            if (CLASS == kClassL) b.lists[4] = mine + smem_table_ints;       // STATE: written and read per insertion step
         }
         replay_group<Team>(p, i, u, cap, base, b, out_col, out_vals, red);
     }
@@ -739,7 +822,8 @@ cudaError_t launch_replay(const SvcProblem& p, const SvcScratch& s, int* out_col
                           int table_ints, int list_ints, cudaStream_t stream) {
     if (groups <= 0) return cudaSuccess;
     auto kern = svc_emit_replay_kernel<Team, CLASS>;
-    const size_t smem = (size_t)Team::kPerBlock * (table_ints + (size_t)kListsPerGroup * list_ints) * sizeof(int);
+    const size_t smem = ((size_t)Team::kPerBlock * (table_ints + (size_t)kListsPerGroup * list_ints) +
+                         (CLASS == kClassL ? kLStateInts : 0)) * sizeof(int);
     static DeviceOnce once;
     if (!once.done()) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
