@@ -19,12 +19,27 @@
 //   epilogue    tcgen05.ld 32 columns at a time -> fp16/fp32 -> 64-byte rows in a swizzled
 //               staging tile -> TMA store (clips the M and N tails, keeps stores off the LSU)
 #include <cuda.h>
+#include <stdio.h>
 #include <stdlib.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
 #include "launch.h"
 #include "ptx.cuh"
+
+#ifdef BLOCK_PROFILE
+// cycles of the MMA-issuing thread, summed over CTAs: waiting for a filled stage, issuing MMAs + commit,
+// waiting for a drained accumulator, whole role; and the number of CTAs
+__device__ unsigned long long g_block_prof[5];
+#define BPROF_DECL long long bp_wait = 0, bp_issue = 0, bp_acc = 0; const long long bp_start = clock64(); long long bp_t = bp_start;
+#define BPROF_ADD(var) { const long long now_ = clock64(); var += now_ - bp_t; bp_t = now_; }
+#define BPROF_FLUSH if (lane == 0) { atomicAdd(&g_block_prof[0], (unsigned long long)bp_wait); atomicAdd(&g_block_prof[1], (unsigned long long)bp_issue); \
+    atomicAdd(&g_block_prof[2], (unsigned long long)bp_acc); atomicAdd(&g_block_prof[3], (unsigned long long)(clock64() - bp_start)); atomicAdd(&g_block_prof[4], 1ull); }
+#else
+#define BPROF_DECL
+#define BPROF_ADD(var)
+#define BPROF_FLUSH
+#endif
 
 namespace sspmm_b200 {
 namespace {
@@ -40,6 +55,7 @@ constexpr int kBlockThreads = 256;
 // replays stopped making progress on B200 (dependents that were launched early sit on SMs and wait).
 // Without the launch attribute the griddepcontrol instructions in the kernels do nothing.
 const int g_block_pdl = (getenv("SSPMM_BLOCK_PDL") != nullptr && getenv("SSPMM_BLOCK_PDL")[0] == '1') ? 1 : 0;
+const bool g_block_wide = !(getenv("SSPMM_BLOCK_WIDE") != nullptr && getenv("SSPMM_BLOCK_WIDE")[0] == '0');
 std::atomic<bool> g_block_pairs{getenv("SSPMM_BLOCK_PAIRS") == nullptr || getenv("SSPMM_BLOCK_PAIRS")[0] != '0'};
 
 // ---- expansion of the compressed operand ------------------------------------
@@ -126,6 +142,8 @@ struct BlockProblem {
     int Mp, N, K;            // rows of C (m_vec*V), columns, reduction length
     int m_tiles, n_tiles, total_tiles;
     int splits, steps_per_split;   // split-K: work item z = split, its K steps [z*steps_per_split, ...); 1 = off
+    int wide;                // 1: the operand maps are chunked ({64, K, width/64[, batch]}), so ONE TMA instruction
+                             // per operand and stage brings all 64-wide chunks; 0: one instruction per chunk
     int64_t out_stride;      // per batch, elements
 };
 
@@ -189,11 +207,16 @@ sspmm_block_kernel(const __grid_constant__ CUtensorMap tmap_at, const __grid_con
                     mbar_arrive_expect_tx(full, L::kAStage + L::kBStage);
                     const uint32_t a_s = sbase + L::kAOff + stage * L::kAStage;
                     const uint32_t b_s = sbase + L::kBOff + stage * L::kBStage;
+                    if (p.wide) {
+                        tma_load_3d(a_s, &tmap_at, 0, ks * kBK, m0 >> 6, full);
+                        tma_load_4d(b_s, &tmap_b, 0, ks * kBK, n0 >> 6, b, full);
+                    } else {
 #pragma unroll
-                    for (int c = 0; c < kBM / 64; ++c) tma_load_2d(a_s + c * L::kChunk, &tmap_at, m0 + 64 * c, ks * kBK, full);
+                        for (int c = 0; c < kBM / 64; ++c) tma_load_2d(a_s + c * L::kChunk, &tmap_at, m0 + 64 * c, ks * kBK, full);
 #pragma unroll
-                    for (int c = 0; c < BN / 64; ++c)
-                        tma_load_3d(b_s + c * L::kChunk, &tmap_b, n0 + 64 * c, ks * kBK, b, full);
+                        for (int c = 0; c < BN / 64; ++c)
+                            tma_load_3d(b_s + c * L::kChunk, &tmap_b, n0 + 64 * c, ks * kBK, b, full);
+                    }
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
                 if (!ok) break;
@@ -203,9 +226,11 @@ sspmm_block_kernel(const __grid_constant__ CUtensorMap tmap_at, const __grid_con
         constexpr uint32_t idesc = make_idesc_f16_f32(kBM, BN, true, true);
         uint32_t stage = 0, phase = 0, acc_it = 0;
         bool ok = true;
+        BPROF_DECL
         for (int T = blockIdx.x; ok && T < p.total_tiles; T += gridDim.x) {
             const uint32_t buf = acc_it & 1u, acc_phase = (acc_it >> 1) & 1u;
             if (!mbar_wait(bar_acc_empty + 8 * buf, acc_phase ^ 1u, abort_flag, kStatusWaitBlock)) break;
+            BPROF_ADD(bp_acc)
             tc_fence_after_sync();
             const uint32_t d_tmem = tmem_base + buf * BN;
             const int z = T / tiles_per_batch;
@@ -213,6 +238,7 @@ sspmm_block_kernel(const __grid_constant__ CUtensorMap tmap_at, const __grid_con
             const int ks1 = p.splits > 1 ? min(k_steps, ks0 + p.steps_per_split) : k_steps;
             for (int ks = ks0; ks < ks1; ++ks) {
                 if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, kStatusWaitBlock)) { ok = false; break; }
+                BPROF_ADD(bp_wait)
                 tc_fence_after_sync();
                 if (lane == 0) {
                     const uint32_t a_s = sbase + L::kAOff + stage * L::kAStage;
@@ -228,6 +254,7 @@ sspmm_block_kernel(const __grid_constant__ CUtensorMap tmap_at, const __grid_con
                     tc_commit(bar_empty + 8 * stage);
                 }
                 __syncwarp();
+                BPROF_ADD(bp_issue)
                 if (++stage == STAGES) { stage = 0; phase ^= 1u; }
             }
             if (!ok) break;
@@ -235,6 +262,7 @@ sspmm_block_kernel(const __grid_constant__ CUtensorMap tmap_at, const __grid_con
             __syncwarp();
             ++acc_it;
         }
+        BPROF_FLUSH
     } else if (warp >= 4) {
         // Each thread owns one row of the 128-row tile.  Per 32 accumulator columns: TMEM -> registers ->
         // 64-byte row pieces in a staging tile (64-byte swizzle, conflict-free) -> one TMA store.
@@ -407,12 +435,17 @@ sspmm_block_pair_kernel(const __grid_constant__ CUtensorMap tmap_at, const __gri
                     const uint32_t full = cluster_map_shared(bar_full + 8 * stage, 0);
                     const uint32_t a_s = sbase + L::kAOff + stage * L::kAStage;
                     const uint32_t b_s = sbase + L::kBOff + stage * L::kBStage;
+                    if (p.wide) {
+                        tma_load_3d_pair(a_s, &tmap_at, 0, ks * kBK, m0 >> 6, full);
+                        tma_load_4d_pair(b_s, &tmap_b, 0, ks * kBK, n0 >> 6, b, full);
+                    } else {
 #pragma unroll
-                    for (int c = 0; c < kBM / 64; ++c)
-                        tma_load_2d_pair(a_s + c * L::kChunk, &tmap_at, m0 + 64 * c, ks * kBK, full);
+                        for (int c = 0; c < kBM / 64; ++c)
+                            tma_load_2d_pair(a_s + c * L::kChunk, &tmap_at, m0 + 64 * c, ks * kBK, full);
 #pragma unroll
-                    for (int c = 0; c < L::kBH / 64; ++c)
-                        tma_load_3d_pair(b_s + c * L::kChunk, &tmap_b, n0 + 64 * c, ks * kBK, b, full);
+                        for (int c = 0; c < L::kBH / 64; ++c)
+                            tma_load_3d_pair(b_s + c * L::kChunk, &tmap_b, n0 + 64 * c, ks * kBK, b, full);
+                    }
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
                 if (!ok) break;
@@ -572,6 +605,20 @@ bool encode_3d(EncodeFn enc, CUtensorMap* m, CUtensorMapDataType dt, size_t es, 
     const cuuint32_t estr[3] = {1u, 1u, 1u};
     return enc(m, dt, 3, const_cast<void*>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// Chunked views for the one-instruction loads: a row-major [rows][width] fp16 matrix (width % 64 == 0) seen as
+// {64, rows, width / 64[, batch]}; a box {64, 64, chunks[, 1]} lands as `chunks` consecutive [64 rows][128 B]
+// swizzled blocks, the layout the MMA descriptors expect.
+bool encode_chunked(EncodeFn enc, CUtensorMap* m, const void* base, uint64_t width, uint64_t rows, uint64_t batch,
+                    uint64_t batch_stride_elems, uint32_t chunks, bool with_batch) {
+    const cuuint64_t gdim[4] = {64, rows, width / 64, batch};
+    const cuuint64_t gstride[3] = {width * 2, 128, (batch > 1 ? batch_stride_elems : width * rows) * 2};
+    const cuuint32_t box[4] = {64, 64, chunks, 1};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    return enc(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, with_batch ? 4 : 3, const_cast<void*>(base), gdim, gstride, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 template <int BN, int STAGES, typename OutT>
@@ -778,9 +825,15 @@ cudaError_t launch_sspmm_block(const SpmmArgs& a, void* scratch, size_t scratch_
     float* partial = split ? reinterpret_cast<float*>(static_cast<uint8_t*>(scratch) + pl.at_bytes) : nullptr;
     const bool c_f16 = a.out_f16 && !split;                       // partial tiles are fp32
     const size_t oes = c_f16 ? 2 : 4;
-    if (!encode_2d(enc, &ta, at, (uint64_t)Mp, (uint64_t)a.K, 64, 64) ||
-        !encode_3d(enc, &tb, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a.rhs, (uint64_t)a.N, (uint64_t)a.K, (uint64_t)a.batch,
-                   (uint64_t)a.rhs_stride, 64, 64, CU_TENSOR_MAP_SWIZZLE_128B) ||
+    // one TMA instruction per operand and stage when both widths are whole 64-element chunks
+    const uint32_t b_chunks = (uint32_t)(pl.pair ? pl.BN / 128 : pl.BN / 64);
+    p.wide = (Mp % 64 == 0 && a.N % 64 == 0 && g_block_wide &&
+              encode_chunked(enc, &ta, at, (uint64_t)Mp, (uint64_t)a.K, 1, 0, 2, false) &&
+              encode_chunked(enc, &tb, a.rhs, (uint64_t)a.N, (uint64_t)a.K, (uint64_t)a.batch, (uint64_t)a.rhs_stride,
+                             b_chunks, true)) ? 1 : 0;
+    if ((!p.wide && (!encode_2d(enc, &ta, at, (uint64_t)Mp, (uint64_t)a.K, 64, 64) ||
+                     !encode_3d(enc, &tb, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a.rhs, (uint64_t)a.N, (uint64_t)a.K,
+                                (uint64_t)a.batch, (uint64_t)a.rhs_stride, 64, 64, CU_TENSOR_MAP_SWIZZLE_128B))) ||
         !encode_3d(enc, &tc, c_f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, oes,
                    split ? static_cast<void*>(partial) : a.out, (uint64_t)a.N, (uint64_t)Mp,
                    (uint64_t)(split ? pl.splits : a.batch), (uint64_t)(split ? (int64_t)Mp * a.N : a.out_stride),
@@ -810,3 +863,15 @@ cudaError_t launch_sspmm_block(const SpmmArgs& a, void* scratch, size_t scratch_
 }
 
 }  // namespace sspmm_b200
+
+#ifdef BLOCK_PROFILE
+extern "C" void block_profile_dump() {
+    unsigned long long h[5];
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(h, g_block_prof, sizeof h);
+    if (h[4]) printf("block kernel MMA thread, mean cycles per CTA over %llu CTAs: wait-full %.0f  issue %.0f  wait-accumulator %.0f  total %.0f\n",
+                     h[4], h[0] / (double)h[4], h[1] / (double)h[4], h[2] / (double)h[4], h[3] / (double)h[4]);
+    unsigned long long z[5] = {0, 0, 0, 0, 0};
+    cudaMemcpyToSymbol(g_block_prof, z, sizeof z);
+}
+#endif
