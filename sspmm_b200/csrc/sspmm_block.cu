@@ -456,9 +456,11 @@ sspmm_block_pair_kernel(const __grid_constant__ CUtensorMap tmap_at, const __gri
             constexpr uint32_t idesc = make_idesc_f16_f32(2 * kBM, BN, true, true);
             uint32_t stage = 0, phase = 0, acc_it = 0;
             bool ok = true;
+            BPROF_DECL
             for (int T = pair; ok && T < p.total_tiles; T += pairs) {
                 const uint32_t buf = acc_it & 1u, acc_phase = (acc_it >> 1) & 1u;
                 if (!mbar_wait(bar_acc_empty + 8 * buf, acc_phase ^ 1u, abort_flag, kStatusWaitBlock)) break;
+                BPROF_ADD(bp_acc)
                 tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + buf * BN;
                 const int z = T / tiles_per_batch;
@@ -466,6 +468,7 @@ sspmm_block_pair_kernel(const __grid_constant__ CUtensorMap tmap_at, const __gri
                 const int ks1 = p.splits > 1 ? min(k_steps, ks0 + p.steps_per_split) : k_steps;
                 for (int ks = ks0; ks < ks1; ++ks) {
                     if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, kStatusWaitBlock)) { ok = false; break; }
+                    BPROF_ADD(bp_wait)
                     tc_fence_after_sync();
                     if (lane == 0) {
                         const uint32_t a_s = sbase + L::kAOff + stage * L::kAStage;
@@ -480,6 +483,7 @@ sspmm_block_pair_kernel(const __grid_constant__ CUtensorMap tmap_at, const __gri
                         tc_commit_pair(bar_empty + 8 * stage, 3);          // the stage is free in both CTAs
                     }
                     __syncwarp();
+                    BPROF_ADD(bp_issue)
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
                 if (!ok) break;
@@ -487,6 +491,7 @@ sspmm_block_pair_kernel(const __grid_constant__ CUtensorMap tmap_at, const __gri
                 __syncwarp();
                 ++acc_it;
             }
+            BPROF_FLUSH
         }
     } else if (warp >= 4) {
         constexpr int kColsPerStore = 64 / (int)sizeof(OutT);
