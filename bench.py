@@ -497,6 +497,45 @@ def kernels_per_product() -> int:
     return 2
 
 
+def _cpu_svc_child(matrix_id, conn):
+    """Child of cpu_svc_all_cores: builds its matrix, waits for the start signal, compresses, reports seconds."""
+    from oracle import svc_oracle
+    a = synthetic.sweep_matrix(matrix_id)
+    rows = a.row_lists()
+    conn.send("ready")
+    conn.recv()
+    t0 = time.perf_counter()
+    svc_oracle.cvse(a.M, a.K, a.nnz, rows, 8)
+    conn.send(time.perf_counter() - t0)
+    conn.close()
+
+
+def cpu_svc_all_cores(ids):
+    """The CPython restatement on independent matrices, one process per matrix (the reference is single-threaded;
+    a sweep can still be split over cores): matrices per second from the common start to the last finish."""
+    import multiprocessing as mp
+    ctx = mp.get_context("spawn")                      # the parent holds a CUDA context: no fork
+    procs = []
+    for i in ids:
+        parent, child = ctx.Pipe()
+        pr = ctx.Process(target=_cpu_svc_child, args=(i, child), daemon=True)
+        pr.start()
+        procs.append((pr, parent))
+    for _, c in procs:
+        if not c.poll(300):
+            raise RuntimeError("CPU SVC worker did not start")
+        c.recv()
+    t0 = time.perf_counter()
+    for _, c in procs:
+        c.send("go")
+    for _, c in procs:
+        c.recv()
+    wall = time.perf_counter() - t0
+    for pr, _ in procs:
+        pr.join(30)
+    return len(ids) / wall
+
+
 def bench_svc(torch, ops, dev, ids=(0, 1, 2, 3, 4, 5, 6, 7)):
     """SVC throughput on a sample of the power-law sweep (V=8): device-resident,
     through the host-buffer entry point, and the CPU oracle on one core."""
@@ -551,11 +590,17 @@ def bench_svc(torch, ops, dev, ids=(0, 1, 2, 3, 4, 5, 6, 7)):
     for a, rows in zip(mats, row_lists):
         svc_oracle.cvse(a.M, a.K, a.nnz, rows, 8)
     t_cpu = time.perf_counter() - t0
+    try:
+        cpu_all = cpu_svc_all_cores(list(ids))
+    except Exception as exc:  # pragma: no cover - depends on the host
+        sys.stderr.write(f"all-core CPU SVC measurement skipped: {exc}\n")
+        cpu_all = None
     return {"sample": f"sweep matrices {list(ids)} (n = {[a.M for a in mats]}), V=8",
             "device_matrices_per_s": len(mats) / t_dev, "device_gbs": nbytes / t_dev / 1e9,
             "device_batched_matrices_per_s": len(mats) / t_batch, "speedup_batched_vs_cpu": t_cpu / t_batch,
             "python_entry_point_matrices_per_s": len(mats) / t_host_api,
             "cpu_oracle_matrices_per_s_1core": len(mats) / t_cpu, "speedup_device_vs_cpu": t_cpu / t_dev,
+            "cpu_oracle_matrices_per_s_one_process_per_matrix": cpu_all, "cpu_cores": os.cpu_count(),
             "spmm_n128": spmm}
 
 
