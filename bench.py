@@ -563,6 +563,18 @@ def bench_svc(torch, ops, dev, ids=(0, 1, 2, 3, 4, 5, 6, 7)):
         ops.svc_batch(batch_in, 8)
     torch.cuda.synchronize()
     t_batch = (time.perf_counter() - t0) / 3
+    # larger stack: 32 matrices in one pass (the long vector rows of different matrices replay side by side)
+    more = [synthetic.sweep_matrix(i) for i in range(len(ids), 32)]
+    batch32 = batch_in + [(torch.from_numpy(a.row_ptr).to(dev), torch.from_numpy(a.col_idx).to(dev),
+                           torch.from_numpy(a.values).to(dev), a.M, a.K) for a in more]
+    ops.svc_batch(batch32, 8)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(3):
+        ops.svc_batch(batch32, 8)
+    torch.cuda.synchronize()
+    t_batch32 = (time.perf_counter() - t0) / 3
+    del batch32, more
     # the SpMM of the same sweep matrices (B = n x 128)
     spmm = []
     for p, c, v, a in dmats:
@@ -598,6 +610,7 @@ def bench_svc(torch, ops, dev, ids=(0, 1, 2, 3, 4, 5, 6, 7)):
     return {"sample": f"sweep matrices {list(ids)} (n = {[a.M for a in mats]}), V=8",
             "device_matrices_per_s": len(mats) / t_dev, "device_gbs": nbytes / t_dev / 1e9,
             "device_batched_matrices_per_s": len(mats) / t_batch, "speedup_batched_vs_cpu": t_cpu / t_batch,
+            "device_batched32_matrices_per_s": 32 / t_batch32,
             "python_entry_point_matrices_per_s": len(mats) / t_host_api,
             "cpu_oracle_matrices_per_s_1core": len(mats) / t_cpu, "speedup_device_vs_cpu": t_cpu / t_dev,
             "cpu_oracle_matrices_per_s_one_process_per_matrix": cpu_all, "cpu_cores": os.cpu_count(),
@@ -614,8 +627,9 @@ def bench_sweep(torch, ops, dev, dist, rank, world, per_rank=8):
               a, torch.randn((a.K, 128), device=dev, dtype=torch.float16)) for a in mats]
 
     def one_pass():
-        for p, c, v, a, B in dmats:
-            vp, vc, vv, _ = ops.svc(p, c, v, a.M, a.K, 8)
+        # the rank's matrices are compressed in one stacked pass, then multiplied one by one
+        parts, _ = ops.svc_batch([(p, c, v, a.M, a.K) for p, c, v, a, B in dmats], 8)
+        for (vp, vc, vv), (p, c, v, a, B) in zip(parts, dmats):
             ops.sspmm(vp, vc, vv, B, 8)
 
     one_pass()
@@ -634,7 +648,7 @@ def bench_sweep(torch, ops, dev, dist, rank, world, per_rank=8):
     return {"matrices": per_rank * world, "matrices_per_rank": per_rank, "seconds_slowest_rank": sec,
             "svc_plus_spmm_matrices_per_s": per_rank * world / sec,
             "useful_tflops_n128": 2.0 * float(nnz.item()) * 128 / sec / 1e12,
-            "note": "matrix_id mod world -> rank; SVC (V=8) then SpMM with B = n x 128 per matrix; weak scaling"}
+            "note": "matrix_id mod world -> rank; SVC (V=8) of the rank's matrices in one stacked pass, then SpMM with B = n x 128 per matrix; weak scaling"}
 
 
 def bench_encoder(torch, dev):
