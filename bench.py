@@ -652,7 +652,7 @@ def bench_sweep(torch, ops, dev, dist, rank, world, per_rank=8):
 
 
 def bench_encoder(torch, dev):
-    """Encoder layer of BASELINE config 4: hidden 768, FFN 3072, 12 heads, seq 512, batch 32, all six weight
+    """Sparse transformer encoder layer: hidden 768, FFN 3072, 12 heads, seq 512, batch 32, all six weight
     matrices pruned to 90 % and compressed at V=16; attention and LayerNorm dense."""
     from sspmm_b200.encoder import SparseEncoderLayer
     layer = SparseEncoderLayer(hidden=768, ffn=3072, heads=12, sparsity=0.9, vec_length=16, device=dev)
