@@ -43,6 +43,22 @@ def test_reader_handles_dlmc_style_files(lib, tmp_path):
     assert len(m.rowInd) == a.nnz and m.rowInd[0] == 0 and m.rowInd[-1] == a.M - 1
 
 
+def test_row_sequence_of_the_reader_behaves_like_the_reference_lists(lib, tmp_path):
+    """colInd_list_array() returns a sequence over the CSR arrays: indexing, negative indices, slices,
+    iteration and comparison give what the reference's list of lists gives."""
+    from sspmm_b200 import sparse_matrix_format as smf
+    a, _ = synthetic.config1()
+    p = str(tmp_path / "c.smtx")
+    smf.write_smtx(p, a.M, a.K, a.nnz, a.row_ptr, a.col_idx)
+    rows = smf.sparse_matrix(p).colInd_list_array()
+    ref = a.row_lists()
+    assert len(rows) == a.M and rows[0] == ref[0] and rows[-1] == ref[-1] and rows[3:7] == ref[3:7]
+    assert [r for r in rows] == ref and rows == ref
+    assert isinstance(rows[5], list)
+    with pytest.raises(IndexError):
+        rows[a.M]
+
+
 def test_empty_matrix_and_errors(lib, tmp_path):
     from sspmm_b200 import capi
     from sspmm_b200 import sparse_matrix_format as smf

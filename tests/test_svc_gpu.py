@@ -195,3 +195,20 @@ def test_svc_batch_equals_one_by_one(lib):
         assert np.array_equal(c.cpu().numpy(), GOLD[n + "/vec_colInd_list"])
         dense = svc_oracle.densify(p.numel() - 1, 8, a.K, p.cpu().tolist(), c.cpu().tolist(), v.cpu().numpy())
         assert np.array_equal(dense[: a.M].view(np.uint16), a.dense().view(np.uint16))
+
+
+def test_reader_rows_take_the_array_path_through_the_python_entry_point(lib, tmp_path):
+    """CVSE fed with the reader's row sequence (CSR arrays handed over without list conversion) equals CVSE fed
+    with plain lists of lists, and both equal the oracle."""
+    from sspmm_b200 import sparse_matrix_format as smf
+    a = synthetic.power_law(3000, np.random.default_rng(77))
+    p = str(tmp_path / "p.smtx")
+    smf.write_smtx(p, a.M, a.K, a.nnz, a.row_ptr, a.col_idx)
+    m = smf.sparse_matrix(p)
+    fast = smf.CVSE(m.M, m.N, m.nnz, m.colInd_list_array(), 8)
+    slow = smf.CVSE(a.M, a.K, a.nnz, a.row_lists(), 8)
+    r = svc_oracle.cvse(a.M, a.K, a.nnz, a.row_lists(), 8)
+    assert fast.vec_row_ptr == slow.vec_row_ptr == r.vec_row_ptr
+    assert fast.vec_colInd_list == slow.vec_colInd_list == r.vec_colInd_list
+    assert fast.tile_num == r.tile_num and fast.vec_colInd_list_array == r.vec_colInd_list_array
+    assert fast.return_TCF_storage() == r.return_TCF_storage() and fast.return_SRBCSR_storage() == r.return_SRBCSR_storage()
