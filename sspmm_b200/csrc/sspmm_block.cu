@@ -637,7 +637,9 @@ cudaError_t launch_block(const SpmmArgs& a, const CUtensorMap& ta, const CUtenso
         if (e != cudaSuccess) return e;
         attr_once.mark();
     }
-    const int grid = p.total_tiles < sms ? p.total_tiles : sms;
+    // as few CTAs as finish in the same number of rounds: the SMs left over go to products on other streams
+    const int rounds = (p.total_tiles + sms - 1) / sms;
+    const int grid = (p.total_tiles + rounds - 1) / rounds;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid); cfg.blockDim = dim3(kBlockThreads); cfg.dynamicSmemBytes = L::kDynamic; cfg.stream = a.stream;
     cudaLaunchAttribute attr[1];
@@ -682,7 +684,8 @@ cudaError_t launch_block_pair(const SpmmArgs& a, const CUtensorMap& ta, const CU
     }
     int cap = (dev >= 0 && dev < 64) ? resident_pairs[dev].load(std::memory_order_acquire) : 0;
     if (cap <= 0 || cap > sms / 2) cap = sms / 2;
-    const int pairs = p.total_tiles < cap ? p.total_tiles : cap;
+    const int rounds = (p.total_tiles + cap - 1) / cap;
+    const int pairs = (p.total_tiles + rounds - 1) / rounds;     // same number of rounds with fewer pairs, see launch_block
     cfg.gridDim = dim3(2 * pairs); cfg.numAttrs = 1 + g_block_pdl;
     return cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, p);
 }
