@@ -1,6 +1,6 @@
-"""Regenerates tests/golden/svc_golden.npz by running the UNMODIFIED reference
-module RowMerge/sparse_matrix_format.py (imported from a reference checkout,
-with a stub standing in for its unused matplotlib import) on seeded synthetic
+"""Regenerates tests/golden/svc_golden.npz (and the fixture tests/golden/tiny_suite.mtx) by running the
+UNMODIFIED reference modules RowMerge/sparse_matrix_format.py and RowMerge/suit_sparse_matrix.py (imported
+from a reference checkout, with a stub standing in for their unused matplotlib import) on seeded synthetic
 inputs.  The reference checkout is only needed to regenerate; the tests read the
 committed .npz.
 
@@ -89,6 +89,28 @@ def main(ref_root: str) -> None:
                 c.CVSE_out(q)
                 out[name + "/cvse_out_sha256"] = np.frombuffer(
                     hashlib.sha256(open(q, "rb").read()).digest(), dtype=np.uint8)
+    # SuiteSparse side: the reference's Matrix Market driver, unmodified, on a small seeded .mtx written
+    # here by scipy (coordinate format with repeated entries, so that the COO -> CSR step sums duplicates)
+    import scipy.io
+    import scipy.sparse
+    import suit_sparse_matrix as ref_suite
+    rng = np.random.default_rng(31)
+    M, K, n = 70, 90, 420
+    coo = scipy.sparse.coo_matrix((rng.uniform(0.5, 1.5, n), (rng.integers(0, M, n), rng.integers(0, K, n))), shape=(M, K))
+    mtx = os.path.join(HERE, "tiny_suite.mtx")
+    scipy.io.mmwrite(mtx, coo, comment="seeded synthetic matrix, see make_golden.py", precision=6)
+    with tempfile.TemporaryDirectory() as d:
+        import shutil
+        os.makedirs(os.path.join(d, "src"))
+        os.makedirs(os.path.join(d, "dst"))
+        shutil.copy(mtx, os.path.join(d, "src", "tiny_suite.mtx"))
+        listing = os.path.join(d, "files.txt")
+        with open(listing, "w") as f:
+            f.write("tiny_suite.mtx\n")
+        for V in (8, 16):
+            ref_suite.generate_suitesparse_CVSE_file(os.path.join(d, "src") + "/", os.path.join(d, "dst") + "/", listing, V)
+            out[f"suite_tiny/cvse_v{V}"] = np.frombuffer(open(os.path.join(d, "dst", "tiny_suite.smtx"), "rb").read(), dtype=np.uint8)
+        out["suite_tiny/csr"] = np.frombuffer(open(os.path.join(d, "src", "tiny_suite_csr.mtx"), "rb").read(), dtype=np.uint8)
     np.savez_compressed(os.path.join(HERE, "svc_golden.npz"), **out)
     print("wrote", len(out), "arrays")
 
