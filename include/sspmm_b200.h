@@ -90,6 +90,17 @@ int sspmm_set_kernel(int which);
  * inside a kernel.  Synchronises the device. */
 int sspmm_device_status(int* status);
 
+/*
+ * Self test of the bounded device-side waits.  Every wait on an mbarrier inside the kernels gives
+ * up after a cycle budget (about two seconds), records a status code and lets the kernel return
+ * instead of spinning.  This call shortens the budget to `limit_cycles` for one launch of a
+ * one-thread kernel that waits on a barrier nobody arrives at, restores the budget, and reports
+ * whether the wait gave up (*gave_up = 1).  Afterwards sspmm_device_status() returns 6 once.
+ * Synchronises the device before and after; nothing traps, faults or spins without bound.
+ * No counterpart in the reference (its kernels have no waits).
+ */
+int sspmm_selftest_wait_expiry(long long limit_cycles, int* gave_up);
+
 /* ------------------------------------------------------------------- SVC --- */
 
 typedef struct svc_job svc_job;

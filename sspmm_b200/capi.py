@@ -21,6 +21,7 @@ SIGNATURES = {
     "sspmm_f16_f16_noalloc": (C.c_int, [C.c_int] * 4 + [_vp] * 7),
     "sspmm_set_kernel": (C.c_int, [C.c_int]),
     "sspmm_device_status": (C.c_int, [c_int_p]),
+    "sspmm_selftest_wait_expiry": (C.c_int, [C.c_longlong, c_int_p]),
     "svc_begin": (C.c_int, [C.c_int] * 3 + [_vp, _vp, _vp, _vp, C.POINTER(_vp), C.POINTER(C.c_int64)]),
     "svc_finish": (C.c_int, [_vp, _vp, _vp, _vp, _vp]),
     "svc_free": (C.c_int, [_vp]),

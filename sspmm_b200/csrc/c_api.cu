@@ -117,6 +117,20 @@ row_swizzle_kernel(int m_vec, const int* __restrict__ row_offsets, int* __restri
     if (i < m_vec) row_indices[rank] = i;
 }
 
+// Wait-expiry self test: one thread waits on an mbarrier that nobody arrives at.  The bounded wait
+// must give up after g_wait_cycle_limit cycles, record kStatusWaitSelfTest and let the kernel return.
+__global__ void wait_expiry_selftest_kernel(int* gave_up) {
+    __shared__ __align__(8) unsigned long long bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        mbar_init(smem_u32(&bar), 1);
+        mbar_fence_init();
+        const bool ok = mbar_wait(smem_u32(&bar), 0, &abort_flag, kStatusWaitSelfTest);
+        *gave_up = ok ? 0 : 1;
+    }
+}
+
 static int spmm_entry(int m_vec, int V, int N, int K, int batch, const int* row_indices, const int* row_offsets,
                       const int* column_indices, const void* values, int64_t values_stride, const void* rhs,
                       int64_t rhs_stride, void* out, int64_t out_stride, bool out_f16, void* stream) {
@@ -255,6 +269,31 @@ int sspmm_device_status(int* status) {
         if (e != cudaSuccess) return fail(e, "status clear");
     }
     return 0;
+}
+
+int sspmm_selftest_wait_expiry(long long limit_cycles, int* gave_up) {
+    g_err[0] = 0;
+    if (!gave_up || limit_cycles <= 0 || limit_cycles > kDefaultWaitCycleLimit) {
+        set_error("limit_cycles must be in (0, %lld] and gave_up non-null", kDefaultWaitCycleLimit);
+        return (int)cudaErrorInvalidValue;
+    }
+    *gave_up = -1;
+    int* d_flag = nullptr;
+    cudaError_t e = cudaDeviceSynchronize();                       // no other kernel of ours sees the short limit
+    if (e == cudaSuccess) e = cudaMalloc(&d_flag, sizeof(int));
+    if (e != cudaSuccess) return fail(e, "self test set-up");
+    e = cudaMemcpyToSymbol(g_wait_cycle_limit, &limit_cycles, sizeof(long long));
+    if (e == cudaSuccess) {
+        wait_expiry_selftest_kernel<<<1, 32>>>(d_flag);
+        e = cudaGetLastError();
+        if (e == cudaSuccess) e = cudaDeviceSynchronize();
+        const long long back = kDefaultWaitCycleLimit;
+        const cudaError_t e2 = cudaMemcpyToSymbol(g_wait_cycle_limit, &back, sizeof(long long));
+        if (e == cudaSuccess) e = e2;
+    }
+    if (e == cudaSuccess) e = cudaMemcpy(gave_up, d_flag, sizeof(int), cudaMemcpyDeviceToHost);
+    cudaFree(d_flag);
+    return e == cudaSuccess ? 0 : fail(e, "wait-expiry self test");
 }
 
 int svc_begin(int M, int K, int vec_length, const int* d_csr_row_ptr, const int* d_csr_col_idx,

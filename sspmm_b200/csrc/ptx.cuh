@@ -15,6 +15,8 @@ enum : int {
     kStatusWaitAccFull = 3,   // epilogue waited for a finished accumulator
     kStatusWaitAccEmpty = 4,  // MMA issuer waited for a drained accumulator
     kStatusWaitBlock = 5,     // block-GEMM kernel wait
+    kStatusWaitSelfTest = 6,  // the wait-expiry self test (a barrier nobody arrives at)
+    kStatusWaitFused = 7,     // fused-loader GEMM kernel wait
 };
 
 // Defined here: the library is built as one translation unit.
@@ -49,8 +51,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
-// Cycle budget of one wait (about two seconds at 2 GHz).
-constexpr long long kWaitCycleLimit = 4000000000LL;
+// Cycle budget of one wait (about two seconds at 2 GHz).  A device variable so that the wait-expiry
+// self test (sspmm_selftest_wait_expiry) can shorten it for its own launch; nothing else writes it.
+constexpr long long kDefaultWaitCycleLimit = 4000000000LL;
+__device__ long long g_wait_cycle_limit = kDefaultWaitCycleLimit;
 
 // Waits for the phase with the given parity to complete.  Returns false when the
 // wait was abandoned: either another thread of the block already raised
@@ -63,7 +67,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         if (mbar_try_wait(bar, parity)) return true;
         if ((it & 63u) == 0u) {
             if (*abort_flag) return false;
-            if (clock64() - t0 > kWaitCycleLimit) {
+            if (clock64() - t0 > g_wait_cycle_limit) {
                 *abort_flag = 1;
                 atomicCAS(&g_device_status, 0, code);
                 return false;
@@ -82,17 +86,6 @@ __device__ __forceinline__ void tc_fence_before_sync() {
 __device__ __forceinline__ void tc_fence_after_sync() {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
-
-// ---- programmatic dependent launch -------------------------------------------
-// A kernel launched with the programmatic-stream-serialization attribute may start while the
-// previous kernel of the stream is still running, once every CTA of that kernel has executed
-// griddep_launch_dependents() (or exited).  Until griddep_wait() returns it must touch nothing the
-// previous kernel (or anything before it that was itself launched early) writes; after it, the
-// previous kernel has completed and its writes are visible.
-__device__ __forceinline__ void griddep_launch_dependents() {
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-}
-__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 // ---- TMA ------------------------------------------------------------------
 __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {

@@ -27,20 +27,6 @@
 #include "launch.h"
 #include "ptx.cuh"
 
-#ifdef BLOCK_PROFILE
-// cycles of the MMA-issuing thread, summed over CTAs: waiting for a filled stage, issuing MMAs + commit,
-// waiting for a drained accumulator, whole role; and the number of CTAs
-__device__ unsigned long long g_block_prof[5];
-#define BPROF_DECL long long bp_wait = 0, bp_issue = 0, bp_acc = 0; const long long bp_start = clock64(); long long bp_t = bp_start;
-#define BPROF_ADD(var) { const long long now_ = clock64(); var += now_ - bp_t; bp_t = now_; }
-#define BPROF_FLUSH if (lane == 0) { atomicAdd(&g_block_prof[0], (unsigned long long)bp_wait); atomicAdd(&g_block_prof[1], (unsigned long long)bp_issue); \
-    atomicAdd(&g_block_prof[2], (unsigned long long)bp_acc); atomicAdd(&g_block_prof[3], (unsigned long long)(clock64() - bp_start)); atomicAdd(&g_block_prof[4], 1ull); }
-#else
-#define BPROF_DECL
-#define BPROF_ADD(var)
-#define BPROF_FLUSH
-#endif
-
 namespace sspmm_b200 {
 namespace {
 
@@ -48,15 +34,9 @@ constexpr int kBM = 128;
 constexpr int kBK = 64;
 constexpr int kBlockThreads = 256;
 
-// Process-wide switch for the CTA-pair kernel (tests and profiling compare the two variants).
-// Programmatic dependent launch between expansion, GEMM and reduction is OFF unless SSPMM_BLOCK_PDL=1:
-// it saves about 1 us per product when products run one after another on one stream, nothing when
-// independent products run on several streams, and with eight streams of such chains in one CUDA graph
-// replays stopped making progress on B200 (dependents that were launched early sit on SMs and wait).
-// Without the launch attribute the griddepcontrol instructions in the kernels do nothing.
-const int g_block_pdl = (getenv("SSPMM_BLOCK_PDL") != nullptr && getenv("SSPMM_BLOCK_PDL")[0] == '1') ? 1 : 0;
-const bool g_block_wide = !(getenv("SSPMM_BLOCK_WIDE") != nullptr && getenv("SSPMM_BLOCK_WIDE")[0] == '0');
-std::atomic<bool> g_block_pairs{getenv("SSPMM_BLOCK_PAIRS") == nullptr || getenv("SSPMM_BLOCK_PAIRS")[0] != '0'};
+// Process-wide switch for the CTA-pair kernel (tests and profiling compare the two variants through
+// sspmm_set_kernel).  Every launch of this file is an ordinary stream-ordered launch.
+std::atomic<bool> g_block_pairs{true};
 
 // ---- expansion of the compressed operand ------------------------------------
 // At[k][i*V .. i*V+V) = values of the vector of row i at column k, or zeros.
@@ -71,11 +51,6 @@ __global__ void __launch_bounds__(256)
 expand_transposed_kernel(int m_vec, int K, const int* __restrict__ row_offsets, const int* __restrict__ col,
                          const __half* __restrict__ values, __half* __restrict__ at) {
     __shared__ int slot[kExpandChunk];
-    // Reading the compressed operand (caller input) may overlap the tail of the previous kernel of the
-    // stream; At may still be read by that kernel (the previous product's GEMM), so it is written only
-    // after griddep_wait().  The GEMM of this product may start its prologue right away.
-    griddep_launch_dependents();
-    bool waited = false;
     const int64_t mp = (int64_t)m_vec * V;
     const int k_begin = blockIdx.x * kExpandChunk;
     const int k_end = min(K, k_begin + kExpandChunk);
@@ -104,7 +79,6 @@ expand_transposed_kernel(int m_vec, int K, const int* __restrict__ row_offsets, 
 #pragma unroll
                 for (int h = 0; h < V / 8; ++h) v[q][h] = js[q] >= 0 ? __ldg(src + h) : make_uint4(0, 0, 0, 0);
             }
-            if (!waited) { griddep_wait(); waited = true; }      // values are in registers: only the stores wait
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
                 const int kq = k + q * (int)blockDim.x;
@@ -117,7 +91,6 @@ expand_transposed_kernel(int m_vec, int K, const int* __restrict__ row_offsets, 
         }
         __syncthreads();
     }
-    if (!waited) griddep_wait();
 }
 
 template <int BN, int STAGES>
@@ -163,7 +136,6 @@ sspmm_block_kernel(const __grid_constant__ CUtensorMap tmap_at, const __grid_con
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kAbortOff);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-    griddep_launch_dependents();       // the next product's expansion may begin reading its inputs
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(bar_full + 8 * s, 1);
@@ -187,7 +159,6 @@ sspmm_block_kernel(const __grid_constant__ CUtensorMap tmap_at, const __grid_con
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_ptr_smem;
-    griddep_wait();                    // At (and B, C) are touched only from here on
     const int k_steps = (p.K + kBK - 1) / kBK;
     const int tiles_per_batch = p.m_tiles * p.n_tiles;
 
@@ -226,11 +197,9 @@ sspmm_block_kernel(const __grid_constant__ CUtensorMap tmap_at, const __grid_con
         constexpr uint32_t idesc = make_idesc_f16_f32(kBM, BN, true, true);
         uint32_t stage = 0, phase = 0, acc_it = 0;
         bool ok = true;
-        BPROF_DECL
         for (int T = blockIdx.x; ok && T < p.total_tiles; T += gridDim.x) {
             const uint32_t buf = acc_it & 1u, acc_phase = (acc_it >> 1) & 1u;
             if (!mbar_wait(bar_acc_empty + 8 * buf, acc_phase ^ 1u, abort_flag, kStatusWaitBlock)) break;
-            BPROF_ADD(bp_acc)
             tc_fence_after_sync();
             const uint32_t d_tmem = tmem_base + buf * BN;
             const int z = T / tiles_per_batch;
@@ -238,7 +207,6 @@ sspmm_block_kernel(const __grid_constant__ CUtensorMap tmap_at, const __grid_con
             const int ks1 = p.splits > 1 ? min(k_steps, ks0 + p.steps_per_split) : k_steps;
             for (int ks = ks0; ks < ks1; ++ks) {
                 if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, kStatusWaitBlock)) { ok = false; break; }
-                BPROF_ADD(bp_wait)
                 tc_fence_after_sync();
                 if (lane == 0) {
                     const uint32_t a_s = sbase + L::kAOff + stage * L::kAStage;
@@ -254,7 +222,6 @@ sspmm_block_kernel(const __grid_constant__ CUtensorMap tmap_at, const __grid_con
                     tc_commit(bar_empty + 8 * stage);
                 }
                 __syncwarp();
-                BPROF_ADD(bp_issue)
                 if (++stage == STAGES) { stage = 0; phase ^= 1u; }
             }
             if (!ok) break;
@@ -262,7 +229,6 @@ sspmm_block_kernel(const __grid_constant__ CUtensorMap tmap_at, const __grid_con
             __syncwarp();
             ++acc_it;
         }
-        BPROF_FLUSH
     } else if (warp >= 4) {
         // Each thread owns one row of the 128-row tile.  Per 32 accumulator columns: TMEM -> registers ->
         // 64-byte row pieces in a staging tile (64-byte swizzle, conflict-free) -> one TMA store.
@@ -389,7 +355,6 @@ sspmm_block_pair_kernel(const __grid_constant__ CUtensorMap tmap_at, const __gri
     const uint32_t rank = cluster_cta_rank();
     const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
 
-    griddep_launch_dependents();
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(bar_full + 8 * s, 1);            // the even CTA's producer; bytes come from both CTAs
@@ -414,7 +379,6 @@ sspmm_block_pair_kernel(const __grid_constant__ CUtensorMap tmap_at, const __gri
     cluster_sync_all();                // the other CTA's barriers exist before anything is signalled to them
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_ptr_smem;
-    griddep_wait();
     const int k_steps = (p.K + kBK - 1) / kBK;
     const int tiles_per_batch = p.m_tiles * p.n_tiles;        // m_tiles counts 256-row pair tiles here
 
@@ -456,20 +420,17 @@ sspmm_block_pair_kernel(const __grid_constant__ CUtensorMap tmap_at, const __gri
             constexpr uint32_t idesc = make_idesc_f16_f32(2 * kBM, BN, true, true);
             uint32_t stage = 0, phase = 0, acc_it = 0;
             bool ok = true;
-            BPROF_DECL
-            for (int T = pair; ok && T < p.total_tiles; T += pairs) {
+                for (int T = pair; ok && T < p.total_tiles; T += pairs) {
                 const uint32_t buf = acc_it & 1u, acc_phase = (acc_it >> 1) & 1u;
                 if (!mbar_wait(bar_acc_empty + 8 * buf, acc_phase ^ 1u, abort_flag, kStatusWaitBlock)) break;
-                BPROF_ADD(bp_acc)
-                tc_fence_after_sync();
+                    tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + buf * BN;
                 const int z = T / tiles_per_batch;
                 const int ks0 = p.splits > 1 ? z * p.steps_per_split : 0;
                 const int ks1 = p.splits > 1 ? min(k_steps, ks0 + p.steps_per_split) : k_steps;
                 for (int ks = ks0; ks < ks1; ++ks) {
                     if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, kStatusWaitBlock)) { ok = false; break; }
-                    BPROF_ADD(bp_wait)
-                    tc_fence_after_sync();
+                        tc_fence_after_sync();
                     if (lane == 0) {
                         const uint32_t a_s = sbase + L::kAOff + stage * L::kAStage;
                         const uint32_t b_s = sbase + L::kBOff + stage * L::kBStage;
@@ -483,16 +444,14 @@ sspmm_block_pair_kernel(const __grid_constant__ CUtensorMap tmap_at, const __gri
                         tc_commit_pair(bar_empty + 8 * stage, 3);          // the stage is free in both CTAs
                     }
                     __syncwarp();
-                    BPROF_ADD(bp_issue)
-                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
                 if (!ok) break;
                 if (lane == 0) tc_commit_pair(bar_acc_full + 8 * buf, 3);  // both CTAs' epilogues may read D
                 __syncwarp();
                 ++acc_it;
             }
-            BPROF_FLUSH
-        }
+            }
     } else if (warp >= 4) {
         constexpr int kColsPerStore = 64 / (int)sizeof(OutT);
         constexpr int kStoresPerLoad = 32 / kColsPerStore;
@@ -628,7 +587,7 @@ bool encode_chunked(EncodeFn enc, CUtensorMap* m, const void* base, uint64_t wid
 
 template <int BN, int STAGES, typename OutT>
 cudaError_t launch_block(const SpmmArgs& a, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
-                         const BlockProblem& p, int sms) {
+                         const BlockProblem& p, int sms, bool setup_only) {
     using L = BlockLayout<BN, STAGES>;
     auto kern = sspmm_block_kernel<BN, STAGES, OutT>;
     static DeviceOnce attr_once;                      // one flag set per instantiation
@@ -637,23 +596,19 @@ cudaError_t launch_block(const SpmmArgs& a, const CUtensorMap& ta, const CUtenso
         if (e != cudaSuccess) return e;
         attr_once.mark();
     }
+    if (setup_only) return cudaSuccess;
     // as few CTAs as finish in the same number of rounds: the SMs left over go to products on other streams
     const int rounds = (p.total_tiles + sms - 1) / sms;
     const int grid = (p.total_tiles + rounds - 1) / rounds;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(grid); cfg.blockDim = dim3(kBlockThreads); cfg.dynamicSmemBytes = L::kDynamic; cfg.stream = a.stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr; cfg.numAttrs = g_block_pdl;
-    return cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, p);
+    kern<<<grid, kBlockThreads, L::kDynamic, a.stream>>>(ta, tb, tc, p);
+    return cudaGetLastError();
 }
 
 // Launch of the CTA-pair kernel: clusters of two CTAs; the persistent grid holds as many pairs as the
 // device can keep resident (asked from the occupancy calculator once per device and instantiation).
 template <int BN, int STAGES, typename OutT>
 cudaError_t launch_block_pair(const SpmmArgs& a, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc,
-                              const BlockProblem& p, int sms) {
+                              const BlockProblem& p, int sms, bool setup_only) {
     using L = PairLayout<BN, STAGES>;
     auto kern = sspmm_block_pair_kernel<BN, STAGES, OutT>;
     static DeviceOnce attr_once;
@@ -662,16 +617,14 @@ cudaError_t launch_block_pair(const SpmmArgs& a, const CUtensorMap& ta, const CU
     cudaGetDevice(&dev);
     cudaLaunchConfig_t cfg = {};
     cfg.blockDim = dim3(kBlockThreads); cfg.dynamicSmemBytes = L::kDynamic; cfg.stream = a.stream;
-    cudaLaunchAttribute attr[2];
+    cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[1].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
+    cfg.attrs = attr; cfg.numAttrs = 1;
     if (!attr_once.done()) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
         if (e != cudaSuccess) return e;
-        cfg.gridDim = dim3(2 * (sms / 2)); cfg.numAttrs = 1;
+        cfg.gridDim = dim3(2 * (sms / 2));
         int n = 0;
         e = cudaOccupancyMaxActiveClusters(&n, kern, &cfg);
         if (e != cudaSuccess) return e;
@@ -682,11 +635,12 @@ cudaError_t launch_block_pair(const SpmmArgs& a, const CUtensorMap& ta, const CU
         if (dev >= 0 && dev < 64) resident_pairs[dev].store(n, std::memory_order_release);
         attr_once.mark();
     }
+    if (setup_only) return cudaSuccess;
     int cap = (dev >= 0 && dev < 64) ? resident_pairs[dev].load(std::memory_order_acquire) : 0;
     if (cap <= 0 || cap > sms / 2) cap = sms / 2;
     const int rounds = (p.total_tiles + cap - 1) / cap;
     const int pairs = (p.total_tiles + rounds - 1) / rounds;     // same number of rounds with fewer pairs, see launch_block
-    cfg.gridDim = dim3(2 * pairs); cfg.numAttrs = 1 + g_block_pdl;
+    cfg.gridDim = dim3(2 * pairs);
     return cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, p);
 }
 
@@ -694,8 +648,6 @@ cudaError_t launch_block_pair(const SpmmArgs& a, const CUtensorMap& ta, const CU
 template <typename OutT>
 __global__ void __launch_bounds__(256)
 reduce_splits_kernel(const float* __restrict__ partial, OutT* __restrict__ out, int64_t elems, int splits) {
-    griddep_launch_dependents();
-    griddep_wait();
     const int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
     if (i >= elems) return;                                      // elems is a multiple of 4 (N % 8 == 0)
     float4 acc = *reinterpret_cast<const float4*>(partial + i);
@@ -784,6 +736,8 @@ size_t sspmm_block_scratch_bytes(const SpmmArgs& a) {
 
 // `scratch` (scratch_bytes long, owned by the caller) holds the transposed dense copy of A
 // (K * m_vec*V halfs) and, when split-K is used, the fp32 partial tiles after it.
+// Every check and every tensor-map encode comes before the first launch: an error return has
+// enqueued nothing and written nothing to `scratch`.
 cudaError_t launch_sspmm_block(const SpmmArgs& a, void* scratch, size_t scratch_bytes) {
     EncodeFn enc = block_encode_fn();
     if (!enc) {
@@ -796,27 +750,13 @@ cudaError_t launch_sspmm_block(const SpmmArgs& a, void* scratch, size_t scratch_
     }
     const int Mp = a.m_vec * a.V;
     __half* at = static_cast<__half*>(scratch);
-    cudaError_t e;
-    {
-        const int by = a.m_vec < 32768 ? a.m_vec : 32768;
-        const dim3 grid((a.K + kExpandChunk - 1) / kExpandChunk, by);
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = grid; cfg.blockDim = dim3(256); cfg.dynamicSmemBytes = 0; cfg.stream = a.stream;
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[0].val.programmaticStreamSerializationAllowed = 1;
-        cfg.attrs = attr; cfg.numAttrs = g_block_pdl;
-        e = cudaLaunchKernelEx(&cfg, a.V == 16 ? expand_transposed_kernel<16> : expand_transposed_kernel<8>, a.m_vec, a.K,
-                               a.row_offsets, a.column_indices, a.values, at);
-        if (e != cudaSuccess) return e;
-    }
     const int sms = current_device_sm_count();
     if (sms <= 0) return cudaErrorNoDevice;
-    const BlockPlan pl = plan_block(a, sms, scratch_bytes);
-    if (pl.at_bytes > scratch_bytes && (size_t)a.K * Mp * sizeof(__half) > scratch_bytes) {
+    if (!scratch || (size_t)a.K * Mp * sizeof(__half) > scratch_bytes) {
         set_error("scratch too small for the block kernel");
         return cudaErrorInvalidValue;
     }
+    const BlockPlan pl = plan_block(a, sms, scratch_bytes);
     BlockProblem p;
     p.Mp = Mp; p.N = a.N; p.K = a.K;
     p.m_tiles = pl.m_tiles; p.n_tiles = pl.n_tiles;
@@ -830,12 +770,16 @@ cudaError_t launch_sspmm_block(const SpmmArgs& a, void* scratch, size_t scratch_
     p.out_stride = a.out_stride;
     CUtensorMap ta, tb, tc;
     const bool split = pl.splits > 1;
+    if (split && pl.at_bytes + pl.partial_bytes > scratch_bytes) {
+        set_error("scratch too small for the split-K partial tiles");
+        return cudaErrorInvalidValue;
+    }
     float* partial = split ? reinterpret_cast<float*>(static_cast<uint8_t*>(scratch) + pl.at_bytes) : nullptr;
     const bool c_f16 = a.out_f16 && !split;                       // partial tiles are fp32
     const size_t oes = c_f16 ? 2 : 4;
     // one TMA instruction per operand and stage when both widths are whole 64-element chunks
     const uint32_t b_chunks = (uint32_t)(pl.pair ? pl.BN / 128 : pl.BN / 64);
-    p.wide = (Mp % 64 == 0 && a.N % 64 == 0 && g_block_wide &&
+    p.wide = (Mp % 64 == 0 && a.N % 64 == 0 &&
               encode_chunked(enc, &ta, at, (uint64_t)Mp, (uint64_t)a.K, 1, 0, 2, false) &&
               encode_chunked(enc, &tb, a.rhs, (uint64_t)a.N, (uint64_t)a.K, (uint64_t)a.batch, (uint64_t)a.rhs_stride,
                              b_chunks, true)) ? 1 : 0;
@@ -849,37 +793,34 @@ cudaError_t launch_sspmm_block(const SpmmArgs& a, void* scratch, size_t scratch_
         set_error("cuTensorMapEncodeTiled failed (Mp=%d N=%d K=%d batch=%d)", Mp, a.N, a.K, a.batch);
         return cudaErrorInvalidValue;
     }
-    if (pl.pair) {                                                // always 256-column tiles, never split
-        return c_f16 ? launch_block_pair<256, 6, __half>(a, ta, tb, tc, p, sms)
-                     : launch_block_pair<256, 6, float>(a, ta, tb, tc, p, sms);
-    } else if (pl.BN == 256) {
-        e = c_f16 ? launch_block<256, 4, __half>(a, ta, tb, tc, p, sms) : launch_block<256, 4, float>(a, ta, tb, tc, p, sms);
-    } else {
-        e = c_f16 ? launch_block<128, 6, __half>(a, ta, tb, tc, p, sms) : launch_block<128, 6, float>(a, ta, tb, tc, p, sms);
+    // one-time function attributes first (setup_only), then the expansion, then the GEMM
+    auto gemm = [&](bool setup_only) -> cudaError_t {
+        if (pl.pair)                                              // always 256-column tiles, never split
+            return c_f16 ? launch_block_pair<256, 6, __half>(a, ta, tb, tc, p, sms, setup_only)
+                         : launch_block_pair<256, 6, float>(a, ta, tb, tc, p, sms, setup_only);
+        if (pl.BN == 256)
+            return c_f16 ? launch_block<256, 4, __half>(a, ta, tb, tc, p, sms, setup_only)
+                         : launch_block<256, 4, float>(a, ta, tb, tc, p, sms, setup_only);
+        return c_f16 ? launch_block<128, 6, __half>(a, ta, tb, tc, p, sms, setup_only)
+                     : launch_block<128, 6, float>(a, ta, tb, tc, p, sms, setup_only);
+    };
+    cudaError_t e = gemm(true);
+    if (e != cudaSuccess) return e;
+    {
+        const int by = a.m_vec < 32768 ? a.m_vec : 32768;
+        const dim3 grid((a.K + kExpandChunk - 1) / kExpandChunk, by);
+        if (a.V == 16) expand_transposed_kernel<16><<<grid, 256, 0, a.stream>>>(a.m_vec, a.K, a.row_offsets, a.column_indices, a.values, at);
+        else expand_transposed_kernel<8><<<grid, 256, 0, a.stream>>>(a.m_vec, a.K, a.row_offsets, a.column_indices, a.values, at);
+        e = cudaGetLastError();
+        if (e != cudaSuccess) return e;
     }
+    e = gemm(false);
     if (e != cudaSuccess || !split) return e;
     const int64_t elems = (int64_t)Mp * a.N;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)((elems / 4 + 255) / 256)); cfg.blockDim = dim3(256); cfg.stream = a.stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr; cfg.numAttrs = g_block_pdl;
-    if (a.out_f16)
-        return cudaLaunchKernelEx(&cfg, reduce_splits_kernel<__half>, (const float*)partial, static_cast<__half*>(a.out), elems, pl.splits);
-    return cudaLaunchKernelEx(&cfg, reduce_splits_kernel<float>, (const float*)partial, static_cast<float*>(a.out), elems, pl.splits);
+    const unsigned rgrid = (unsigned)((elems / 4 + 255) / 256);
+    if (a.out_f16) reduce_splits_kernel<__half><<<rgrid, 256, 0, a.stream>>>(partial, static_cast<__half*>(a.out), elems, pl.splits);
+    else reduce_splits_kernel<float><<<rgrid, 256, 0, a.stream>>>(partial, static_cast<float*>(a.out), elems, pl.splits);
+    return cudaGetLastError();
 }
 
 }  // namespace sspmm_b200
-
-#ifdef BLOCK_PROFILE
-extern "C" void block_profile_dump() {
-    unsigned long long h[5];
-    cudaDeviceSynchronize();
-    cudaMemcpyFromSymbol(h, g_block_prof, sizeof h);
-    if (h[4]) printf("block kernel MMA thread, mean cycles per CTA over %llu CTAs: wait-full %.0f  issue %.0f  wait-accumulator %.0f  total %.0f\n",
-                     h[4], h[0] / (double)h[4], h[1] / (double)h[4], h[2] / (double)h[4], h[3] / (double)h[4]);
-    unsigned long long z[5] = {0, 0, 0, 0, 0};
-    cudaMemcpyToSymbol(g_block_prof, z, sizeof z);
-}
-#endif

@@ -31,7 +31,6 @@
 //                      table growth steps are replayed level by level (8, 32, 128, ...).
 #include "svc.cuh"
 
-#include <cstdio>
 #include <mutex>
 
 #include "launch.h"
@@ -39,17 +38,6 @@
 namespace sspmm_b200 {
 
 __device__ int g_svc_bad_column = 0;
-
-#ifdef SVC_PROFILE
-__device__ unsigned long long g_svc_prof[8 * 8];     // [class][phase] cycles of thread 0 of each team
-#define PROF_DECL long long prof_t = clock64(); long long prof_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-#define PROF_MARK(ph) { const long long now_ = clock64(); prof_acc[ph] += now_ - prof_t; prof_t = now_; }
-#define PROF_FLUSH(cls) if (Team::tid() == 0) { for (int k_ = 0; k_ < 8; ++k_) atomicAdd(&g_svc_prof[(cls) * 8 + k_], (unsigned long long)prof_acc[k_]); atomicAdd(&g_svc_prof[(cls) * 8 + 7], 1ull); }
-#else
-#define PROF_DECL
-#define PROF_MARK(ph)
-#define PROF_FLUSH(cls)
-#endif
 
 namespace {
 
@@ -593,7 +581,6 @@ __device__ void replay_group(const SvcProblem& p, int i, int u_final, int cap, i
     if (tid < kMinTable) tab[tid] = -1;
     Team::sync();
     bool duplicate = false;
-    PROF_DECL
 
     for (int r = r0; r < r1 && !duplicate; ++r) {
         const int rs = p.row_ptr[r], rlen = p.row_ptr[r + 1] - rs;
@@ -611,7 +598,6 @@ __device__ void replay_group(const SvcProblem& p, int i, int u_final, int cap, i
         Team::sync();
         const int n_total = n_cur + n_new;
         if (n_total > u_final) { duplicate = true; break; }     // only possible when the row repeats a column
-        PROF_MARK(0)
 
         // ---- replay  set(list)  for the sequence  D = x[0..n_cur) ++ fresh[0..n_new), level by level.
         // Inside a level the table length is fixed and insertion is first come, first served: an element
@@ -638,7 +624,6 @@ __device__ void replay_group(const SvcProblem& p, int i, int u_final, int cap, i
                     if (q + b * Team::kSize < n_l) seq[q + b * Team::kSize] = v4[b];
             }
             Team::sync();
-            PROF_MARK(2)
             const int first_new = max(e_len, n_cur);
             bool dup_here = false;          // also raised when a bound is hit: the group is then redone sequentially
             volatile unsigned* vstate = state;
@@ -675,7 +660,6 @@ __device__ void replay_group(const SvcProblem& p, int i, int u_final, int cap, i
               }
             }
             Team::sync();
-            PROF_MARK(3)
             if (Team::any(dup_here, red)) { duplicate = true; break; }
             if (n_total < trig) {
                 // no further growth: this table is final; keys in place, ordered list out
@@ -689,7 +673,6 @@ __device__ void replay_group(const SvcProblem& p, int i, int u_final, int cap, i
         if (duplicate) break;
         int* t2 = x; x = xn; xn = t2;
         mask_prev = mask;
-        PROF_MARK(4)
     }
 
     if (duplicate) {
@@ -733,8 +716,6 @@ __device__ void replay_group(const SvcProblem& p, int i, int u_final, int cap, i
         }
     }
     Team::sync();
-    PROF_MARK(5)
-    PROF_FLUSH(replay_class(u_final, cap))
 }
 
 template <class Team, int CLASS>
@@ -839,13 +820,6 @@ cudaError_t launch_replay(const SvcProblem& p, const SvcScratch& s, int* out_col
     const long long cap_blocks = (long long)sms * (smem > 100 * 1024 ? 1 : (smem > 40 * 1024 ? 3 : 6));
     int grid = (int)(want < cap_blocks ? want : cap_blocks);
     if (grid < 1) grid = 1;
-#ifdef SVC_PROFILE
-    {
-        int nb = -1;
-        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, kern, Team::kSize * Team::kPerBlock, smem);
-        printf("replay class %d: groups %lld grid %d smem %zu occupancy %d blocks/SM\n", CLASS, groups, grid, smem, nb);
-    }
-#endif
     kern<<<grid, Team::kSize * Team::kPerBlock, smem, stream>>>(p, s.vec_ptr, s.tbl_len, s.tbl_off, s.tables, out_col,
                                                                  out_vals, table_ints, list_ints);
     return cudaGetLastError();
@@ -933,22 +907,6 @@ cudaError_t svc_emit(const SvcProblem& p, const SvcScratch& s, const long long* 
     return f.join();
 }
 
-#ifdef SVC_PROFILE
-extern "C" void svc_profile_dump() {
-    unsigned long long h[64];
-    cudaDeviceSynchronize();
-    cudaMemcpyFromSymbol(h, g_svc_prof, sizeof h);
-    const char* names[6] = {"new", "seqprefix", "level-setup", "rounds", "extract", "values"};
-    for (int c = 1; c < 6; ++c) {
-        if (!h[c * 8 + 7]) continue;
-        printf("class %d groups %llu:", c, h[c * 8 + 7]);
-        for (int k = 0; k < 6; ++k) printf(" %s=%.1fus", names[k], h[c * 8 + k] / 1.9e3 / (double)h[c * 8 + 7]);
-        printf("  (per group)\n");
-    }
-    unsigned long long z[64] = {0};
-    cudaMemcpyToSymbol(g_svc_prof, z, sizeof z);
-}
-#endif
 
 cudaError_t svc_read_and_clear_bad_column_flag(int* flag, cudaStream_t stream) {
     cudaError_t e = cudaMemcpyFromSymbolAsync(flag, g_svc_bad_column, sizeof(int), 0, cudaMemcpyDeviceToHost, stream);
