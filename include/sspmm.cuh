@@ -2,7 +2,9 @@
 // against SSpMM/include/sspmm.cuh (e.g. SSpMM/sspmm_test.cpp:141,189) compiles
 // and links against libsspmm_b200.so unchanged.  Every overload forwards to the
 // C ABI in sspmm_b200.h on the legacy default stream and returns its status as
-// a cudaError_t; work is asynchronous, nothing is allocated.
+// a cudaError_t.  Unlike the reference's kernel these calls may take scratch from
+// the stream-ordered allocator and synchronise once per new row_offsets pointer;
+// sspmm_b200.h ("What the regular entry points do behind the call") has the details.
 //
 // The driver passes (m_vec, vec_length, N, K) to BOTH families below
 // (SSpMM/sspmm_test.cpp:141 and :189), whatever the parameter names say, so

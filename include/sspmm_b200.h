@@ -35,7 +35,8 @@ extern "C" {
  * row_indices (may be NULL) is a permutation of 0..m_vec-1 giving the order in
  * which vector rows are scheduled (the reference's row swizzle,
  * SSpMM/include/bm_test_utils.h:206-225); it never changes the result.
- * Asynchronous on `stream`; allocates nothing; keeps no state.
+ * Asynchronous on `stream` except for the first call with a given row_offsets pointer; see
+ * "What the regular entry points do behind the call" below for allocation and remembered state.
  */
 int sspmm_f16_f32(int m_vec, int vec_length, int N, int K, const int* row_indices, const int* row_offsets,
                   const int* column_indices, const void* values_f16, const void* rhs_f16, float* out_f32,
@@ -62,7 +63,7 @@ int sspmm_f16_f16_batched(int m_vec, int vec_length, int N, int K, int batch, co
  * Same product as sspmm_f16_f16, for callers that must not allocate device memory when they call:
  * a server that gave all device memory to its own arena at start-up, or a latency-critical loop
  * in which an allocation could fail or stall other streams.  No counterpart in the reference (its
- * kernels need no scratch).  Always runs the block kernel; its scratch (a dense transposed copy of
+ * kernel needs no scratch).  Always runs the block kernel; its scratch (a dense transposed copy of
  * A) lives in a fixed array inside the library image, so
  *   - K * m_vec * vec_length * 2 must not exceed SSPMM_NOALLOC_MAX_SCRATCH_BYTES, K > 0,
  *     N % 8 == 0, values / rhs / out 16-byte aligned; anything else is rejected with an error;
@@ -77,6 +78,85 @@ int sspmm_f16_f16_batched(int m_vec, int vec_length, int N, int K, int batch, co
 int sspmm_f16_f16_noalloc(int m_vec, int vec_length, int N, int K, const int* row_indices, const int* row_offsets,
                           const int* column_indices, const void* values_f16, const void* rhs_f16, void* out_f16,
                           void* stream);
+
+/*
+ * What the regular entry points (sspmm_f16_f32, sspmm_f16_f16, sspmm_f16_f16_batched) do behind the
+ * call.  The reference's kernel needs no scratch and its driver owns every buffer
+ * (SSpMM/sspmm_test.cpp:108-127, 256-262); these entry points keep that signature but not that
+ * property:
+ *   - the choice between the row-gather kernel and the block kernel needs nvec = row_offsets[m_vec]
+ *     on the host.  It is read with a device-to-host copy and a synchronisation of `stream` the
+ *     first time a (row_offsets pointer, m_vec, device) triple is seen and remembered in a table of
+ *     64 entries keyed by that triple.  A freed and re-used pointer therefore gets the previous
+ *     matrix's nvec: the result is still right (every kernel accepts every operand), only the
+ *     choice of kernel may be the slower one.  While `stream` is being captured nothing is read
+ *     and the row-gather kernel is used;
+ *   - the block kernel takes K * m_vec*V * 2 bytes (a dense transposed copy of A), plus fp32
+ *     partial tiles when it splits K, from cudaMallocAsync on `stream` and returns them with
+ *     cudaFreeAsync; the row-gather kernel does the same for the partial tiles of split long rows;
+ *   - once per device the release threshold of the device's default memory pool is raised to 1 GiB
+ *     so that this scratch is not returned to the system at every synchronisation.
+ * Callers that must not allocate or synchronise at call time use a plan (below), or
+ * sspmm_f16_f16_noalloc.
+ */
+
+/* --------------------------------------------- plans and groups (one launch) --- */
+
+/*
+ * The entry points above follow the reference's calling convention, which has no place for anything
+ * computed ahead of time: they must work for whatever arrays they are handed, so for dense-ish
+ * matrices they expand A into scratch from the stream-ordered allocator and launch two or three
+ * kernels (see "What the regular entry points do behind the call" at the end of this header).
+ * A PLAN is the ahead-of-time part: built once per weight STRUCTURE (row_offsets and
+ * column_indices, which must stay alive and unchanged while the plan is used; the VALUES may
+ * change between calls), it lets the product run as ONE kernel launch straight from the compressed
+ * operand, with no scratch, no allocation and no host synchronisation at call time.
+ * The reference has no counterpart (its kernel, SSpMM/src/sspmm.cu:548-649, needs none: one launch,
+ * no scratch); a maintainer of SSpMM/sspmm_test.cpp would create the plan after the cudaMemcpy calls
+ * at :120-127 and call sspmm_planned in the timed loop at :189.
+ *
+ * sspmm_plan_create reads nvec, allocates the plan's device metadata (16 bytes per vector row and 64
+ * columns, plus 4 bytes per vector when some row's column list is not ascending) and synchronises
+ * `stream` twice.  Structures that are too sparse for dense tiles (fewer than 1/16 of the
+ * (vector row, column) slots filled), or irregular (a column listed twice in a vector row, a column
+ * id outside [0, K)), get a plan without metadata: sspmm_planned then forwards to
+ * sspmm_f16_f16 / sspmm_f16_f32, and such a plan cannot join a group.
+ */
+typedef struct sspmm_plan sspmm_plan;
+int sspmm_plan_create(int m_vec, int vec_length, int K, const int* d_row_offsets, const int* d_column_indices,
+                      void* stream, sspmm_plan** plan);
+int sspmm_plan_destroy(sspmm_plan* plan);
+/* Any output pointer may be NULL.  one_launch = 1 when the plan carries metadata. */
+int sspmm_plan_info(const sspmm_plan* plan, int64_t* nvec, int* one_launch, int* ascending, int64_t* device_bytes);
+
+/* out[m_vec*V][N] = A_vs * rhs[K][N] with the plan's structure: one launch on `stream`, nothing
+ * allocated, no host synchronisation (N % 8 == 0; values, rhs, out 16-byte aligned; out fp16 when
+ * out_is_f16 != 0, else fp32). */
+int sspmm_planned(const sspmm_plan* plan, const void* values_f16, const void* rhs_f16, void* out, int N, int out_is_f16,
+                  void* stream);
+
+/*
+ * A GROUP binds several products (the layers of a model step, the members of a batch) to their
+ * operands and runs all of them as ONE persistent launch: the tiles of all products form one work
+ * list, longest first, taken by the CTAs from a shared queue, so that small products fill the SMs a
+ * large one leaves idle; tiles with a long K range are cut into parts whose fp32 partial tiles are
+ * added, in part order, by whichever part finishes last.  sspmm_group_create allocates the
+ * descriptors and that scratch once (and synchronises); sspmm_group_run allocates nothing.
+ * Operand pointers are fixed at creation.  A group must not run twice at the same time (its queue and
+ * scratch are single-use per launch), and the current device must be the one it was created on.
+ */
+typedef struct sspmm_group sspmm_group;
+typedef struct sspmm_group_item {
+    const sspmm_plan* plan;
+    const void* values_f16;
+    const void* rhs_f16;   /* [K][N] */
+    void* out;             /* [m_vec*V][N] */
+    int N;
+} sspmm_group_item;
+int sspmm_group_create(const sspmm_group_item* items, int count, int out_is_f16, sspmm_group** group);
+int sspmm_group_run(sspmm_group* group, void* stream);
+int sspmm_group_info(const sspmm_group* group, int* tile_columns, int* work_items, int* ctas, int64_t* scratch_bytes);
+int sspmm_group_destroy(sspmm_group* group);
 
 /* Kernel selection for the calls above: 0 = automatic (default), 1 = tensor-core
  * row-gather kernel fed by TMA gather requests (error if the operands do not qualify),

@@ -19,6 +19,14 @@ SIGNATURES = {
     "sspmm_f16_f16": (C.c_int, [C.c_int] * 4 + [_vp] * 7),
     "sspmm_f16_f16_batched": (C.c_int, [C.c_int] * 5 + [_vp, _vp, _vp, _vp, C.c_int64, _vp, C.c_int64, _vp, C.c_int64, _vp]),
     "sspmm_f16_f16_noalloc": (C.c_int, [C.c_int] * 4 + [_vp] * 7),
+    "sspmm_plan_create": (C.c_int, [C.c_int] * 3 + [_vp, _vp, _vp, C.POINTER(_vp)]),
+    "sspmm_plan_destroy": (C.c_int, [_vp]),
+    "sspmm_plan_info": (C.c_int, [_vp, C.POINTER(C.c_int64), c_int_p, c_int_p, C.POINTER(C.c_int64)]),
+    "sspmm_planned": (C.c_int, [_vp, _vp, _vp, _vp, C.c_int, C.c_int, _vp]),
+    "sspmm_group_create": (C.c_int, [_vp, C.c_int, C.c_int, C.POINTER(_vp)]),
+    "sspmm_group_run": (C.c_int, [_vp, _vp]),
+    "sspmm_group_info": (C.c_int, [_vp, c_int_p, c_int_p, c_int_p, C.POINTER(C.c_int64)]),
+    "sspmm_group_destroy": (C.c_int, [_vp]),
     "sspmm_set_kernel": (C.c_int, [C.c_int]),
     "sspmm_device_status": (C.c_int, [c_int_p]),
     "sspmm_selftest_wait_expiry": (C.c_int, [C.c_longlong, c_int_p]),
@@ -34,6 +42,11 @@ SIGNATURES = {
     "sspmm_last_error_string": (C.c_char_p, []),
     "sspmm_version": (C.c_char_p, []),
 }
+
+
+class GroupItem(C.Structure):
+    """struct sspmm_group_item of include/sspmm_b200.h."""
+    _fields_ = [("plan", _vp), ("values_f16", _vp), ("rhs_f16", _vp), ("out", _vp), ("N", C.c_int)]
 
 
 class SspmmError(RuntimeError):

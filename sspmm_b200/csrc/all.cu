@@ -4,6 +4,7 @@
 #include "sspmm_gather_lsu.cu"
 #include "sspmm_simt.cu"
 #include "sspmm_block.cu"
+#include "sspmm_fused.cu"
 #include "svc.cu"
 #include "c_api.cu"
 #include "cxx_api.cu"

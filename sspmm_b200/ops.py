@@ -150,3 +150,105 @@ def sorted_row_swizzle(row_offsets: torch.Tensor) -> torch.Tensor:
     with torch.cuda.device(row_offsets.device):
         capi.check(capi.lib().sspmm_sorted_row_swizzle(m_vec, row_offsets.data_ptr(), out.data_ptr(), _stream_ptr()))
     return out
+
+
+class Plan:
+    """Ahead-of-time part of the SpMM for one weight structure (``sspmm_plan_create``): with it the product runs
+    as one kernel launch straight from the compressed operand, without scratch, allocation or host
+    synchronisation.  Keeps ``row_offsets`` and ``column_indices`` alive; the values may change between calls."""
+
+    def __init__(self, row_offsets: torch.Tensor, column_indices: torch.Tensor, vec_length: int, K: int):
+        import ctypes as C
+        _require(row_offsets, torch.int32, "row_offsets")
+        _require(column_indices, torch.int32, "column_indices")
+        self.row_offsets, self.column_indices = row_offsets, column_indices
+        self.V, self.K = vec_length, K
+        self.m_vec = row_offsets.numel() - 1
+        self.device = row_offsets.device
+        self._h = C.c_void_p()
+        with torch.cuda.device(self.device):
+            capi.check(capi.lib().sspmm_plan_create(self.m_vec, vec_length, K, row_offsets.data_ptr(),
+                                                    column_indices.data_ptr(), _stream_ptr(), C.byref(self._h)))
+        nvec, one, asc, nbytes = C.c_int64(), C.c_int(), C.c_int(), C.c_int64()
+        capi.check(capi.lib().sspmm_plan_info(self._h, C.byref(nvec), C.byref(one), C.byref(asc), C.byref(nbytes)))
+        self.nvec, self.one_launch, self.ascending, self.device_bytes = nvec.value, bool(one.value), bool(asc.value), nbytes.value
+
+    @property
+    def handle(self):
+        return self._h
+
+    def close(self) -> None:
+        if self._h:
+            capi.lib().sspmm_plan_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def sspmm_planned(plan: Plan, values: torch.Tensor, rhs: torch.Tensor, out_dtype=torch.float16,
+                  out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """C = A_vs @ rhs through ``sspmm_planned``: one launch, nothing allocated by the library."""
+    _require(values, torch.float16, "values")
+    _require(rhs, torch.float16, "rhs")
+    K, N = rhs.shape
+    if K != plan.K:
+        raise ValueError(f"rhs has {K} rows, the plan was built for K = {plan.K}")
+    if out is None:
+        out = torch.empty((plan.m_vec * plan.V, N), dtype=out_dtype, device=rhs.device)
+    with torch.cuda.device(rhs.device):
+        rc = capi.lib().sspmm_planned(plan.handle, values.data_ptr(), rhs.data_ptr(), out.data_ptr(), N,
+                                      1 if out.dtype == torch.float16 else 0, _stream_ptr())
+    if rc != 0:
+        capi.check(rc)
+    return out
+
+
+class Group:
+    """Several products bound to their operands and run as ONE persistent launch (``sspmm_group_create`` /
+    ``sspmm_group_run``).  ``products`` is a list of (plan, values, rhs, out); all outputs share one dtype."""
+
+    def __init__(self, products):
+        import ctypes as C
+        if not products:
+            raise ValueError("a group needs at least one product")
+        self._keep = list(products)
+        out_dtype = products[0][3].dtype
+        arr = (capi.GroupItem * len(products))()
+        for i, (plan, values, rhs, out) in enumerate(products):
+            _require(values, torch.float16, "values")
+            _require(rhs, torch.float16, "rhs")
+            _require(out, out_dtype, "out")
+            if rhs.shape[0] != plan.K or tuple(out.shape) != (plan.m_vec * plan.V, rhs.shape[1]):
+                raise ValueError(f"product {i}: operand shapes do not match the plan")
+            arr[i] = capi.GroupItem(plan.handle, values.data_ptr(), rhs.data_ptr(), out.data_ptr(), rhs.shape[1])
+        self.device = products[0][2].device
+        self._h = C.c_void_p()
+        with torch.cuda.device(self.device):
+            capi.check(capi.lib().sspmm_group_create(arr, len(products), 1 if out_dtype == torch.float16 else 0, C.byref(self._h)))
+        bn, items, ctas, nbytes = C.c_int(), C.c_int(), C.c_int(), C.c_int64()
+        capi.check(capi.lib().sspmm_group_info(self._h, C.byref(bn), C.byref(items), C.byref(ctas), C.byref(nbytes)))
+        self.tile_columns, self.work_items, self.ctas, self.scratch_bytes = bn.value, items.value, ctas.value, nbytes.value
+
+    def run(self) -> None:
+        if torch.cuda.current_device() == self.device.index:
+            rc = capi.lib().sspmm_group_run(self._h, _stream_ptr())
+        else:
+            with torch.cuda.device(self.device):
+                rc = capi.lib().sspmm_group_run(self._h, _stream_ptr())
+        if rc != 0:
+            capi.check(rc)
+
+    def close(self) -> None:
+        if self._h:
+            capi.lib().sspmm_group_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
