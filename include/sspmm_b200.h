@@ -137,13 +137,22 @@ int sspmm_planned(const sspmm_plan* plan, const void* values_f16, const void* rh
 
 /*
  * A GROUP binds several products (the layers of a model step, the members of a batch) to their
- * operands and runs all of them as ONE persistent launch: the tiles of all products form one work
- * list, longest first, taken by the CTAs from a shared queue, so that small products fill the SMs a
- * large one leaves idle; tiles with a long K range are cut into parts whose fp32 partial tiles are
- * added, in part order, by whichever part finishes last.  sspmm_group_create allocates the
- * descriptors and that scratch once (and synchronises); sspmm_group_run allocates nothing.
- * Operand pointers are fixed at creation.  A group must not run twice at the same time (its queue and
- * scratch are single-use per launch), and the current device must be the one it was created on.
+ * operands and runs all of them as one persistent tensor-core launch: the tiles of all products
+ * form one work list, longest first, taken by the CTAs from a shared queue, so that small products
+ * fill the SMs a large one leaves idle; tiles with a long K range are cut into parts whose fp32
+ * partial tiles are added, in part order, by whichever part finishes last.
+ * mode 1 (compressed): the A tiles are built inside the kernel from the compressed operand; one
+ *     launch per run and no scratch for A;
+ * mode 2 (expanded): every run first writes dense transposed copies of the A operands (one extra
+ *     launch for the whole group, K * m_vec*V * 2 bytes per product, owned by the group) and the
+ *     tensor-core kernel fetches its A tiles from them by TMA: about a third less time per K step,
+ *     which pays off once every SM has a few dozen K steps of work;
+ * mode 0: chosen from the amount of work per SM.
+ * sspmm_group_create allocates the descriptors and the scratch once (and synchronises);
+ * sspmm_group_run allocates nothing and does not synchronise.  Operand pointers are fixed at
+ * creation; the contents of every operand, the values included, may change between runs.  A group
+ * must not run twice at the same time (its queue and scratch serve one run at a time), and the
+ * current device must be the one it was created on.
  */
 typedef struct sspmm_group sspmm_group;
 typedef struct sspmm_group_item {
@@ -153,9 +162,11 @@ typedef struct sspmm_group_item {
     void* out;             /* [m_vec*V][N] */
     int N;
 } sspmm_group_item;
-int sspmm_group_create(const sspmm_group_item* items, int count, int out_is_f16, sspmm_group** group);
+int sspmm_group_create(const sspmm_group_item* items, int count, int out_is_f16, int mode, sspmm_group** group);
 int sspmm_group_run(sspmm_group* group, void* stream);
-int sspmm_group_info(const sspmm_group* group, int* tile_columns, int* work_items, int* ctas, int64_t* scratch_bytes);
+/* Any output pointer may be NULL.  launches = kernels per run (1 or 2). */
+int sspmm_group_info(const sspmm_group* group, int* tile_columns, int* work_items, int* ctas, int* launches,
+                     int64_t* scratch_bytes);
 int sspmm_group_destroy(sspmm_group* group);
 
 /* Kernel selection for the calls above: 0 = automatic (default), 1 = tensor-core
@@ -205,6 +216,27 @@ int svc_begin(int M, int K, int vec_length, const int* d_csr_row_ptr, const int*
               const void* d_csr_values_f16, void* stream, svc_job** job, int64_t* nvec);
 int svc_finish(svc_job* job, int* d_vec_row_ptr, int* d_vec_col, void* d_vec_values_f16, void* stream);
 int svc_free(svc_job* job);
+
+/*
+ * The same compression for a BATCH of independent matrices in one pass (a sweep over many
+ * matrices, RowMerge/sparse_matrix_format.py:199-237 and RowMerge/suit_sparse_matrix.py:199-216
+ * loop over them one by one).  HOST arrays of `count` sizes and of `count` DEVICE pointers;
+ * d_csr_values_f16 may be NULL (structure only, as the reference).  The matrices are stacked on the
+ * device and compressed together; svc_batch_begin returns each matrix's vector count in nvec[count]
+ * (synchronises `stream`), svc_batch_finish writes the results of all matrices one after another:
+ *   d_vec_row_ptr   sum(m_vec_i + 1) ints, matrix i's pointers starting again at 0
+ *   d_vec_col       sum(nvec_i) ints          d_vec_values   sum(nvec_i) * V fp16 (or NULL)
+ * so matrix i's pieces start at the running sums of (m_vec + 1), nvec and nvec * V.  Column order
+ * inside every vector row is the reference's, as in svc_begin.
+ */
+typedef struct svc_batch_job svc_batch_job;
+int svc_batch_begin(int count, int vec_length, const int* M, const int* K, const int* nnz,
+                    const int* const* d_csr_row_ptr, const int* const* d_csr_col_idx, const void* const* d_csr_values_f16,
+                    void* stream, svc_batch_job** job, int64_t* nvec);
+int svc_batch_finish(svc_batch_job* job, int* d_vec_row_ptr, int* d_vec_col, void* d_vec_values_f16, void* stream);
+int svc_batch_free(svc_batch_job* job);
+/* Vector rows of the whole batch that needed the hash-order replay; valid after svc_batch_begin. */
+int svc_batch_replayed_rows(svc_batch_job* job, int64_t* rows);
 
 /* Number of vector rows whose column order needed the hash-order replay (the
  * others are ascending); diagnostic, valid after svc_begin. */

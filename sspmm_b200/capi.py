@@ -23,9 +23,9 @@ SIGNATURES = {
     "sspmm_plan_destroy": (C.c_int, [_vp]),
     "sspmm_plan_info": (C.c_int, [_vp, C.POINTER(C.c_int64), c_int_p, c_int_p, C.POINTER(C.c_int64)]),
     "sspmm_planned": (C.c_int, [_vp, _vp, _vp, _vp, C.c_int, C.c_int, _vp]),
-    "sspmm_group_create": (C.c_int, [_vp, C.c_int, C.c_int, C.POINTER(_vp)]),
+    "sspmm_group_create": (C.c_int, [_vp, C.c_int, C.c_int, C.c_int, C.POINTER(_vp)]),
     "sspmm_group_run": (C.c_int, [_vp, _vp]),
-    "sspmm_group_info": (C.c_int, [_vp, c_int_p, c_int_p, c_int_p, C.POINTER(C.c_int64)]),
+    "sspmm_group_info": (C.c_int, [_vp, c_int_p, c_int_p, c_int_p, c_int_p, C.POINTER(C.c_int64)]),
     "sspmm_group_destroy": (C.c_int, [_vp]),
     "sspmm_set_kernel": (C.c_int, [C.c_int]),
     "sspmm_device_status": (C.c_int, [c_int_p]),
@@ -33,6 +33,11 @@ SIGNATURES = {
     "svc_begin": (C.c_int, [C.c_int] * 3 + [_vp, _vp, _vp, _vp, C.POINTER(_vp), C.POINTER(C.c_int64)]),
     "svc_finish": (C.c_int, [_vp, _vp, _vp, _vp, _vp]),
     "svc_free": (C.c_int, [_vp]),
+    "svc_batch_begin": (C.c_int, [C.c_int, C.c_int, c_int_p, c_int_p, c_int_p, C.POINTER(_vp), C.POINTER(_vp), C.POINTER(_vp), _vp,
+                                  C.POINTER(_vp), C.POINTER(C.c_int64)]),
+    "svc_batch_finish": (C.c_int, [_vp, _vp, _vp, _vp, _vp]),
+    "svc_batch_free": (C.c_int, [_vp]),
+    "svc_batch_replayed_rows": (C.c_int, [_vp, C.POINTER(C.c_int64)]),
     "svc_reorder": (C.c_int, [C.c_int] * 3 + [_vp] * 4),
     "svc_replayed_rows": (C.c_int, [_vp, C.POINTER(C.c_int64)]),
     "sspmm_sorted_row_swizzle": (C.c_int, [C.c_int, _vp, _vp, _vp]),

@@ -8,6 +8,7 @@
 #include <cstring>
 #include <mutex>
 #include <new>
+#include <vector>
 
 #include "../../include/sspmm_b200.h"
 #include "launch.h"
@@ -223,6 +224,17 @@ struct svc_job {
     cudaStream_t stream;
 };
 
+struct svc_batch_job {
+    int count, V;
+    long long rows, entries, vec_rows;
+    bool with_values;
+    svc_job* inner;              // the compression of the stacked matrix
+    void* block;                 // table, cuts and the stacked CSR
+    SvcBatchEntry* d_tab;
+    long long* d_cuts;
+    cudaStream_t stream;
+};
+
 extern "C" {
 
 int sspmm_f16_f32(int m_vec, int vec_length, int N, int K, const int* row_indices, const int* row_offsets,
@@ -385,6 +397,133 @@ int svc_free(svc_job* j) {
     if (j->s.tables) cudaFreeAsync(j->s.tables, j->stream);
     if (j->s.vec_ptr) cudaFreeAsync(j->s.vec_ptr, j->stream);
     delete j;
+    return 0;
+}
+
+int svc_batch_begin(int count, int vec_length, const int* M, const int* K, const int* nnz,
+                    const int* const* d_csr_row_ptr, const int* const* d_csr_col_idx, const void* const* d_csr_values_f16,
+                    void* stream, svc_batch_job** job, int64_t* nvec) {
+    g_err[0] = 0;
+    if (!job || !nvec) { set_error("null output pointer"); return (int)cudaErrorInvalidValue; }
+    *job = nullptr;
+    if (count <= 0 || !M || !K || !nnz || !d_csr_row_ptr || !d_csr_col_idx) {
+        set_error("a batch needs at least one matrix and its size arrays");
+        return (int)cudaErrorInvalidValue;
+    }
+    if (vec_length != 8 && vec_length != 16) {
+        set_error("vec_length must be 8 or 16 (got %d)", vec_length);
+        return (int)cudaErrorInvalidValue;
+    }
+    const int V = vec_length;
+    std::vector<SvcBatchEntry> tab((size_t)count + 1);
+    long long rows = 0, entries = 0, vec_rows = 0;
+    int k_max = 0;
+    bool with_values = d_csr_values_f16 != nullptr;
+    for (int i = 0; i < count; ++i) {
+        if (M[i] < 0 || K[i] < 0 || nnz[i] < 0 || !d_csr_row_ptr[i] || (nnz[i] > 0 && !d_csr_col_idx[i])) {
+            set_error("matrix %d: bad size or null array", i);
+            return (int)cudaErrorInvalidValue;
+        }
+        if (with_values && nnz[i] > 0 && !d_csr_values_f16[i]) with_values = false;
+        const long long mv = (M[i] + V - 1) / V;
+        tab[i] = SvcBatchEntry{d_csr_row_ptr[i], d_csr_col_idx[i], with_values ? static_cast<const __half*>(d_csr_values_f16[i]) : nullptr,
+                               rows, entries, vec_rows, M[i], nnz[i]};
+        rows += mv * V; entries += nnz[i]; vec_rows += mv;
+        if (K[i] > k_max) k_max = K[i];
+    }
+    tab[count] = SvcBatchEntry{nullptr, nullptr, nullptr, rows, entries, vec_rows, 0, 0};
+    if (rows >= 0x7fffffffLL || entries >= 0x7fffffffLL) {
+        set_error("stacked batch does not fit 32-bit indices (%lld rows, %lld entries)", rows, entries);
+        return (int)cudaErrorInvalidValue;
+    }
+    if (k_max > kSvcMaxK) {
+        set_error("K = %d exceeds the supported maximum of %d columns", k_max, kSvcMaxK);
+        return (int)cudaErrorInvalidValue;
+    }
+    svc_batch_job* b = new (std::nothrow) svc_batch_job();
+    if (!b) return (int)cudaErrorMemoryAllocation;
+    b->count = count; b->V = V; b->rows = rows; b->entries = entries; b->vec_rows = vec_rows; b->with_values = with_values;
+    b->inner = nullptr; b->block = nullptr;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // one allocation: table | cuts[count+1] (int64) | stacked row_ptr | stacked col | stacked values
+    auto up = [](size_t x) { return (x + 255) & ~(size_t)255; };
+    const size_t off_cuts = up(tab.size() * sizeof(SvcBatchEntry));
+    const size_t off_ptr = off_cuts + up(((size_t)count + 1) * 8);
+    const size_t off_col = off_ptr + up(((size_t)rows + 1) * 4);
+    const size_t off_val = off_col + up((size_t)entries * 4);
+    const size_t total = off_val + (with_values ? up((size_t)entries * 2) : 0);
+    keep_pool_memory();
+    cudaError_t e = cudaMallocAsync(&b->block, total, st);
+    if (e != cudaSuccess) { delete b; return fail(e, "batch scratch allocation"); }
+    uint8_t* base = static_cast<uint8_t*>(b->block);
+    b->d_tab = reinterpret_cast<SvcBatchEntry*>(base);
+    b->d_cuts = reinterpret_cast<long long*>(base + off_cuts);
+    int* s_ptr = reinterpret_cast<int*>(base + off_ptr);
+    int* s_col = reinterpret_cast<int*>(base + off_col);
+    __half* s_val = with_values ? reinterpret_cast<__half*>(base + off_val) : nullptr;
+    e = cudaMemcpyAsync(b->d_tab, tab.data(), tab.size() * sizeof(SvcBatchEntry), cudaMemcpyHostToDevice, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);          // `tab` is pageable host memory about to go out of scope
+    if (e == cudaSuccess) e = svc_stack(b->d_tab, count, rows, entries, V, s_ptr, s_col, s_val, st);
+    int64_t total_nvec = 0;
+    int rc = 0;
+    if (e == cudaSuccess) {
+        rc = svc_begin((int)rows, k_max, V, s_ptr, s_col, s_val, stream, &b->inner, &total_nvec);
+        if (rc == 0) {
+            e = svc_batch_cuts(b->d_tab, count, b->inner->s.vec_ptr, b->d_cuts, st);
+            std::vector<long long> cuts((size_t)count + 1);
+            if (e == cudaSuccess) e = cudaMemcpyAsync(cuts.data(), b->d_cuts, cuts.size() * 8, cudaMemcpyDeviceToHost, st);
+            if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+            if (e == cudaSuccess)
+                for (int i = 0; i < count; ++i) nvec[i] = cuts[i + 1] - cuts[i];
+        }
+    }
+    if (e != cudaSuccess || rc != 0) {
+        if (b->inner) svc_free(b->inner);
+        cudaFreeAsync(b->block, st);
+        delete b;
+        return rc != 0 ? rc : fail(e, "batch stacking");
+    }
+    b->stream = st;
+    *job = b;
+    return 0;
+}
+
+int svc_batch_finish(svc_batch_job* b, int* d_vec_row_ptr, int* d_vec_col, void* d_vec_values_f16, void* stream) {
+    g_err[0] = 0;
+    if (!b || !d_vec_row_ptr) { set_error("null pointer"); return (int)cudaErrorInvalidValue; }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    svc_job* j = b->inner;
+    // vector row pointers of each matrix, rebased to start at 0, one after another
+    cudaError_t e = svc_batch_row_ptrs(b->d_tab, b->count, b->vec_rows, j->s.vec_ptr, b->d_cuts, d_vec_row_ptr, st);
+    if (e != cudaSuccess) return fail(e, "row pointer rebase");
+    if (j->nvec == 0) return 0;
+    if (!d_vec_col) { set_error("null pointer"); return (int)cudaErrorInvalidValue; }
+    __half* ov = j->with_values ? static_cast<__half*>(d_vec_values_f16) : nullptr;
+    if (ov) {
+        e = cudaMemsetAsync(ov, 0, (size_t)j->nvec * j->p.V * sizeof(__half), st);
+        if (e != cudaSuccess) return fail(e, "value clear");
+    }
+    if (j->table_ints > 0 && !j->s.tables) {
+        e = cudaMallocAsync(reinterpret_cast<void**>(&j->s.tables), (size_t)j->table_ints * 4, st);
+        if (e != cudaSuccess) return fail(e, "table scratch allocation");
+    }
+    e = svc_emit(j->p, j->s, j->class_groups, d_vec_col, ov, st);
+    if (e != cudaSuccess) return fail(e, "SVC emit");
+    j->stream = st;
+    b->stream = st;
+    return 0;
+}
+
+int svc_batch_replayed_rows(svc_batch_job* b, int64_t* rows) {
+    if (!b || !b->inner) return (int)cudaErrorInvalidValue;
+    return svc_replayed_rows(b->inner, rows);
+}
+
+int svc_batch_free(svc_batch_job* b) {
+    if (!b) return 0;
+    if (b->inner) svc_free(b->inner);
+    if (b->block) cudaFreeAsync(b->block, b->stream);
+    delete b;
     return 0;
 }
 

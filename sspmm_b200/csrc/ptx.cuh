@@ -51,6 +51,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
+// Non-blocking form: has the phase with the given parity completed?
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
 // Cycle budget of one wait (about two seconds at 2 GHz).  A device variable so that the wait-expiry
 // self test (sspmm_selftest_wait_expiry) can shorten it for its own launch; nothing else writes it.
 constexpr long long kDefaultWaitCycleLimit = 4000000000LL;

@@ -10,19 +10,21 @@
 // step and every vector row of the tile, a 64-bit mask of the columns that carry a vector and the
 // position of the first of them in column order (16 bytes).  A loader thread that owns slot (vector
 // row, column k) of a stage then knows, without reading a column id, whether a vector exists and where:
-// values[start + popc(mask below k)], through a permutation when the row's list is not ascending.
+// values[start + popc(mask below k)].  When some row's column list is not ascending the plan holds the positions
+// themselves instead (4 bytes per slot), laid out so that a loader thread reads its own in one or two loads.
 //
 // Per CTA (persistent, one per SM), tile 128 rows x BN columns, K step 64:
-//   warp 0        TMA producer of the B tile [64 k][BN n] (N-major, 128-byte swizzle)
+//   warp 0        one thread: scheduler (takes work items -- static stride, or an atomic queue shared by the grid --
+//                 and publishes them to the other warps through a shared-memory ring, well ahead of their use)
+//                 and TMA producer of the B tile [64 k][BN n] (N-major, 128-byte swizzle)
 //   warp 1        MMA issuer / TMEM owner: tcgen05.mma kind::f16, M = 128, N <= BN, K = 16, accumulators
 //                 2 x BN TMEM columns
-//   warp 2        scheduler: takes work items (static stride, or an atomic queue shared by the grid) and
-//                 publishes them to the other warps through a small shared-memory ring
 //   warps 4-7     epilogue: TMEM -> registers -> swizzled staging -> TMA store; or, for a tile whose K range
 //                 was cut into parts, fp32 partial tile to scratch and the LAST part to arrive adds all parts
 //                 in part order and writes C (no CTA ever waits for another)
 //   warps 8-15    two loader groups that build the A tile [64 k][128 m] (M-major, 128-byte swizzle) of
-//                 alternate stages from the value vectors with 16-byte loads and stores
+//                 alternate stages from the value vectors: 16-byte loads into registers, requested well
+//                 ahead of the 16-byte stores into the tile
 // Every wait is bounded and unwinds with a status code (see ptx.cuh).
 #include <cuda.h>
 #include <cuda_fp16.h>
@@ -41,22 +43,35 @@ namespace fused {
 
 constexpr int kBM = 128;
 constexpr int kBK = 64;
-constexpr int kThreads = 512;
-constexpr int kRing = 4;
+// Warps: 0 scheduler + TMA producer (one thread), 1 MMA issuer, 2-3 idle, 4-7 epilogue, 8-15 two loader groups
+// of four warps.  Sixteen warps are four per scheduler partition: 128 registers per thread.  (Measured on B200:
+// a third loader group caps every thread at 96 registers and made the kernel slower, not faster.)
 constexpr int kLoaderGroups = 2;
 constexpr int kGroupThreads = 128;
+constexpr int kEpilogueWarp0 = 4;
+constexpr int kLoaderWarp0 = 8;
+constexpr int kPublishAhead = 16;       // items the scheduler keeps published ahead of the B producer (< kRing)
+constexpr int kThreads = kLoaderWarp0 * 32 + kLoaderGroups * kGroupThreads;
+// Work items are published ahead of their use.  A loader thread looks four of its own stages ahead, which with
+// one-step items is a dozen items past the stage it is about to store, while the epilogue may still hold the
+// item two before that one; the scheduler keeps kPublishAhead items published beyond the one the B producer is
+// loading, and the ring is deeper than both spans together, so a loader never waits for an item that could
+// only be published after the loader itself has stored.
+constexpr int kRing = 32;
 
 // One product, as the kernel sees it.  Lives in kernel parameter space (single product) or in device
 // memory (group); 64-byte aligned because of the tensor maps.
 struct alignas(64) Problem {
+    CUtensorMap tmap_a;        // expanded mode only: At {M', K, 1} fp16 (dense transposed copy of A), box 64 x 64, 128-byte swizzle
     CUtensorMap tmap_b;        // B  {N, K, 1}   fp16, box 64 x 64, 128-byte swizzle
     CUtensorMap tmap_c;        // C  {N, M', 1}  fp16/fp32, box (64 bytes) x 128 rows, 64-byte swizzle
-    const uint4* meta;         // plan: [m_tile][k_step][row in tile] {mask lo, mask hi, start, 0}
-    const int* perm;           // plan: position in column order -> index of the vector (null = identity)
+    const uint4* meta;         // plan, ascending rows: [m_tile][k_step][row in tile] {mask lo, mask hi, start, 0}
+    const int* posmap;         // plan, other structures: [m_tile][k_step][loader thread][slot] index of the vector or -1
     const __half* values;
     void* out;
     int Mp, N, K, V;
-    int k_steps, m_tiles, n_tiles, reserved;
+    int k_steps, m_tiles, n_tiles;
+    int wide;                  // bit 0: tmap_b, bit 1: tmap_a are chunked views {64, rows, width / 64}: one TMA request brings all chunks of a tile
 };
 static_assert(sizeof(Problem) % 64 == 0, "Problem must keep the tensor maps 64-byte aligned in arrays");
 
@@ -78,17 +93,20 @@ struct Params {
     Problem inline_prob;
 };
 
+// Shared memory: a ring of stages, each an A tile (filled by the loader warps, or by TMA) and a B tile (filled
+// by TMA); one tcgen05.commit per K step releases both.
 template <int BN, int STAGES>
 struct Layout {
+    static constexpr int kAStages = STAGES, BSTAGES = STAGES;
     static constexpr int kAStage = kBM * kBK * 2;                // 16 KB: 2 chunks of [64 k][64 m]
     static constexpr int kBStage = BN * kBK * 2;                 // BN/64 chunks of [64 k][64 n]
     static constexpr int kChunk = kBK * 128;                     // 8 KB
     static constexpr int kAOff = 0;
-    static constexpr int kBOff = STAGES * kAStage;
+    static constexpr int kBOff = kAStages * kAStage;
     static constexpr int kOutBuf = kBM * 64;                     // 128 rows x 64 bytes
-    static constexpr int kOutOff = kBOff + STAGES * kBStage;
+    static constexpr int kOutOff = kBOff + BSTAGES * kBStage;
     static constexpr int kBarOff = kOutOff + 2 * kOutBuf;
-    static constexpr int kNumBars = 2 * STAGES + 4 + 2 * kRing;
+    static constexpr int kNumBars = 3 * STAGES + 4 + 2 * kRing;
     static constexpr int kRingOff = kBarOff + kNumBars * 8;
     static constexpr int kTmemPtrOff = kRingOff + kRing * 32;
     static constexpr int kAbortOff = kTmemPtrOff + 8;
@@ -96,6 +114,7 @@ struct Layout {
     static constexpr int kBytes = kBcastOff + 8;
     static constexpr int kDynamic = kBytes + 1024;
     static constexpr uint32_t kTmemCols = 2 * BN;                // 128, 256 or 512
+    static_assert(kDynamic <= 227 * 1024, "shared memory of one CTA");
 };
 
 __device__ __forceinline__ void fence_tensormap_acquire(const void* tmap) {
@@ -103,41 +122,38 @@ __device__ __forceinline__ void fence_tensormap_acquire(const void* tmap) {
     asm volatile("fence.proxy.tensormap::generic.acquire.sys [%0], 128;" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");
 }
 
-// Loads the value vectors of one A stage (vector rows of tile m_tile, columns [64 ks, 64 ks + 64)) into
-// registers: thread t of the 128 of a loader group owns vector row t / TPR and columns t % TPR + TPR * q.
+// The A tile of one stage (vector rows of tile m_tile, columns [64 ks, 64 ks + 64)) is built by the 128
+// threads of a loader group: thread t owns vector row t / TPR and columns t % TPR + TPR * q.  Positions,
+// loads and stores are separate steps so that a loader keeps several stages in flight (see the loader role).
 template <int V>
-struct AStage {
+struct ATile {
     static constexpr int R = kBM / V;             // vector rows per tile: 8 or 16
     static constexpr int TPR = kGroupThreads / R; // threads per vector row: 16 or 8
     static constexpr int SLOTS = kBK / TPR;       // columns per thread: 4 or 8
     static constexpr int H = V / 8;               // 16-byte pieces per vector: 2 or 1
-    uint4 v[SLOTS][H];
 
-    __device__ __forceinline__ void load(const Problem* P, uint4 meta, int t) {
+    // positions of this thread's vectors in the value array (-1: no vector) from the row's column mask
+    static __device__ __forceinline__ void positions(uint4 meta, int t, int (&jj)[8]) {
         const unsigned long long mask = (unsigned long long)meta.x | ((unsigned long long)meta.y << 32);
         const int start = (int)meta.z;
         const int kb = t % TPR;
-        int jj[SLOTS];
 #pragma unroll
         for (int q = 0; q < SLOTS; ++q) {
             const int kk = kb + TPR * q;
             const bool present = (mask >> kk) & 1ull;
             jj[q] = present ? start + __popcll(mask & ((1ull << kk) - 1ull)) : -1;
         }
-        if (P->perm) {
-#pragma unroll
-            for (int q = 0; q < SLOTS; ++q)
-                if (jj[q] >= 0) jj[q] = __ldg(P->perm + jj[q]);
-        }
+    }
+    static __device__ __forceinline__ void load(const __half* __restrict__ values, const int (&jj)[8], uint4 (&v)[8]) {
 #pragma unroll
         for (int q = 0; q < SLOTS; ++q) {
-            const uint4* src = reinterpret_cast<const uint4*>(P->values + (int64_t)(jj[q] >= 0 ? jj[q] : 0) * V);
+            const uint4* src = reinterpret_cast<const uint4*>(values + (int64_t)(jj[q] >= 0 ? jj[q] : 0) * V);
 #pragma unroll
-            for (int h = 0; h < H; ++h) v[q][h] = jj[q] >= 0 ? __ldg(src + h) : make_uint4(0u, 0u, 0u, 0u);
+            for (int h = 0; h < H; ++h) v[q * H + h] = jj[q] >= 0 ? __ldg(src + h) : make_uint4(0u, 0u, 0u, 0u);
         }
     }
     // a_s: the stage's A tile; rows of 128 bytes (64 m of one k), 16-byte pieces XOR-swizzled by k & 7
-    __device__ __forceinline__ void store(uint8_t* a_s, int t) const {
+    static __device__ __forceinline__ void store(uint8_t* a_s, int t, const uint4 (&v)[8]) {
         const int r = t / TPR, kb = t % TPR;
         uint8_t* base = a_s + (r / (R / 2)) * (kBK * 128);
         const int piece0 = (r % (R / 2)) * H;
@@ -146,23 +162,32 @@ struct AStage {
             const int kk = kb + TPR * q;
 #pragma unroll
             for (int h = 0; h < H; ++h)
-                *reinterpret_cast<uint4*>(base + kk * 128 + (((piece0 + h) ^ (kk & 7)) << 4)) = v[q][h];
+                *reinterpret_cast<uint4*>(base + kk * 128 + (((piece0 + h) ^ (kk & 7)) << 4)) = v[q * H + h];
         }
-    }
-    static __device__ __forceinline__ uint4 load_meta(const Problem* P, int m_tile, int ks, int t) {
-        return __ldg(P->meta + ((int64_t)m_tile * P->k_steps + ks) * R + t / TPR);
     }
 };
 
-template <int BN, int STAGES, typename OutT>
+// One stage of the CTA's stage sequence, as a loader thread carries it while the stage is in flight.
+struct StageDesc {
+    const __half* values;
+    int V;               // 8 or 16, + 32 when the metadata words are positions; 0 = no stage (end of the sequence)
+};
+
+// ATMA = true: the A tiles come by TMA from a dense transposed copy of A (written by expand_group_kernel just
+// before; the loader warps then have nothing to do).  ATMA = false: the loader warps build them from the
+// compressed operand.
+template <int BN, int STAGES, typename OutT, bool ATMA>
 __global__ void __launch_bounds__(kThreads, 1)
 sspmm_fused_kernel(const __grid_constant__ Params gp) {
     using L = Layout<BN, STAGES>;
+    constexpr int kAStages = STAGES, BSTAGES = STAGES;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     const uint32_t sbase = smem_u32(smem);
-    const uint32_t bar_full = sbase + L::kBarOff;
-    const uint32_t bar_empty = bar_full + STAGES * 8;
+    const uint32_t bar_a_full = sbase + L::kBarOff;          // A tile of the stage written (loader warps; unused with A by TMA)
+    const uint32_t bar_b_full = bar_a_full + STAGES * 8;      // B tile (and, with A by TMA, the A tile) of the stage has landed
+    const uint32_t bar_empty = bar_b_full + STAGES * 8;       // the MMAs that read the stage have completed
+    const uint32_t bar_a_empty = bar_empty, bar_b_empty = bar_empty;
     const uint32_t bar_acc_full = bar_empty + STAGES * 8;
     const uint32_t bar_acc_empty = bar_acc_full + 2 * 8;
     const uint32_t bar_item_full = bar_acc_empty + 2 * 8;
@@ -175,7 +200,8 @@ sspmm_fused_kernel(const __grid_constant__ Params gp) {
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
-            mbar_init(bar_full + 8 * s, 1 + kGroupThreads / 32);   // producer's expect_tx + the loader group's warps
+            mbar_init(bar_a_full + 8 * s, kGroupThreads / 32);     // the warps of the loader group that owns the stage
+            mbar_init(bar_b_full + 8 * s, 1);                      // producer's expect_tx
             mbar_init(bar_empty + 8 * s, 1);                       // tcgen05.commit
         }
         for (int b = 0; b < 2; ++b) {
@@ -184,7 +210,7 @@ sspmm_fused_kernel(const __grid_constant__ Params gp) {
         }
         for (int r = 0; r < kRing; ++r) {
             mbar_init(bar_item_full + 8 * r, 1);
-            mbar_init(bar_item_empty + 8 * r, 14);                 // warps 0, 1, 4-7, 8-15
+            mbar_init(bar_item_empty + 8 * r, 6 + (ATMA ? 0 : kLoaderGroups * kGroupThreads / 32));   // producer, MMA, epilogue and loader warps
         }
         *abort_flag = 0;
         mbar_fence_init();
@@ -214,70 +240,103 @@ sspmm_fused_kernel(const __grid_constant__ Params gp) {
         return it.prob >= 0;
     };
 
-    if (warp == 2) {
-        // ------------------------------------------------------------------ scheduler
+    if (warp < 4) {
+      if (warp == 0) {
+        // ------------------------------------------------------------------ scheduler + TMA producer of B
         if (lane == 0) {
-            int idx = blockIdx.x;
-            for (uint32_t n = 0;; ++n) {
-                const uint32_t slot = n % kRing, ph = (n / kRing) & 1u;
-                if (!mbar_wait(bar_item_empty + 8 * slot, ph ^ 1u, abort_flag, kStatusWaitFused)) break;
-                Item it;
-                if (idx < gp.n_items) {
-                    if (gp.items) {
-                        const int4* src = reinterpret_cast<const int4*>(gp.items + idx);
-                        const int4 lo = __ldg(src), hi = __ldg(src + 1);
-                        it.prob = lo.x; it.m_tile = lo.y; it.n_tile = lo.z; it.ks0 = lo.w;
-                        it.ks1 = hi.x; it.pslot = hi.y; it.pp = hi.z; it.cslot = hi.w;
-                    } else {
-                        it.prob = 0; it.m_tile = idx % gp.inline_prob.m_tiles; it.n_tile = idx / gp.inline_prob.m_tiles;
-                        it.ks0 = 0; it.ks1 = gp.inline_prob.k_steps; it.pslot = 0; it.pp = 1 << 8; it.cslot = 0;
+            // scheduler state: items 0 .. n_pub-1 of this CTA are in the ring; raw_next is the answer of the
+            // queue to the request made when the previous item was published (used only at the next publish,
+            // so the thread does not wait for it)
+            uint32_t n_pub = 0;
+            bool sched_done = false;
+            int idx = blockIdx.x, raw_next = 0;
+            // publishes items until `upto` are in the ring (or the list ends); must = false: gives up when the ring is full
+            auto publish = [&](uint32_t upto, bool must) -> bool {
+                while (!sched_done && n_pub < upto) {
+                    const uint32_t slot = n_pub % kRing, ph = (n_pub / kRing) & 1u;
+                    if (must) {
+                        if (!mbar_wait(bar_item_empty + 8 * slot, ph ^ 1u, abort_flag, kStatusWaitFused)) return false;
+                    } else if (!mbar_test_wait(bar_item_empty + 8 * slot, ph ^ 1u)) {
+                        return true;
                     }
-                } else {
-                    it.prob = -1; it.m_tile = it.n_tile = it.ks0 = it.ks1 = it.pslot = it.pp = it.cslot = 0;
+                    if (n_pub > 0) idx = gp.dynamic ? (int)gridDim.x + raw_next : idx + (int)gridDim.x;
+                    Item it;
+                    if (idx < gp.n_items) {
+                        if (gp.items) {
+                            const int4* src = reinterpret_cast<const int4*>(gp.items + idx);
+                            const int4 lo = __ldg(src), hi = __ldg(src + 1);
+                            it.prob = lo.x; it.m_tile = lo.y; it.n_tile = lo.z; it.ks0 = lo.w;
+                            it.ks1 = hi.x; it.pslot = hi.y; it.pp = hi.z; it.cslot = hi.w;
+                        } else {
+                            it.prob = 0; it.m_tile = idx % gp.inline_prob.m_tiles; it.n_tile = idx / gp.inline_prob.m_tiles;
+                            it.ks0 = 0; it.ks1 = gp.inline_prob.k_steps; it.pslot = 0; it.pp = 1 << 8; it.cslot = 0;
+                        }
+                    } else {
+                        it.prob = -1; it.m_tile = it.n_tile = it.ks0 = it.ks1 = it.pslot = it.pp = it.cslot = 0;
+                    }
+                    volatile int* e = ring + slot * 8;
+                    e[0] = it.prob; e[1] = it.m_tile; e[2] = it.n_tile; e[3] = it.ks0; e[4] = it.ks1;
+                    e[5] = it.pslot; e[6] = it.pp; e[7] = it.cslot;
+                    mbar_arrive(bar_item_full + 8 * slot);
+                    ++n_pub;
+                    if (it.prob < 0) sched_done = true;
+                    else if (gp.dynamic) raw_next = atomicAdd(gp.queue, 1);
                 }
-                volatile int* e = ring + slot * 8;
-                e[0] = it.prob; e[1] = it.m_tile; e[2] = it.n_tile; e[3] = it.ks0; e[4] = it.ks1;
-                e[5] = it.pslot; e[6] = it.pp; e[7] = it.cslot;
-                mbar_arrive(bar_item_full + 8 * slot);
-                if (it.prob < 0) break;
-                idx = gp.dynamic ? (int)gridDim.x + atomicAdd(gp.queue, 1) : idx + (int)gridDim.x;
+                return true;
+            };
+            uint32_t stage = 0, phase = 0;
+            int last_prob = -1;
+            bool ok = true;
+            Item it;
+            for (uint32_t n = 0; ok; ++n) {
+                if (!publish(n + 1, true)) break;                // the item this thread is about to load
+                publish(n + 1 + kPublishAhead, false);           // and, ring permitting, the ones the loaders look ahead to
+                if (!take_item(n, it, false)) break;
+                const Problem* P = problem_of(it.prob);
+                if (gp.probs && it.prob != last_prob) {
+                    fence_tensormap_acquire(&P->tmap_b);
+                    if (ATMA) fence_tensormap_acquire(&P->tmap_a);
+                    last_prob = it.prob;
+                }
+                const int n0 = it.n_tile * BN;
+                const int wide = P->wide;
+                // a chunked request always brings the whole box (chunks past the matrix are zero-filled)
+                const int chunks = (wide & 1) ? BN / 64 : min(BN / 64, (P->N - n0 + 63) >> 6);
+                for (int ks = it.ks0; ks < it.ks1; ++ks) {
+                    if (!mbar_wait(bar_b_empty + 8 * stage, phase ^ 1u, abort_flag, kStatusWaitFused)) { ok = false; break; }
+                    const uint32_t full = bar_b_full + 8 * stage;
+                    mbar_arrive_expect_tx(full, (uint32_t)chunks * L::kChunk + (ATMA ? L::kAStage : 0));
+                    if constexpr (ATMA) {
+                        const uint32_t a_s = sbase + L::kAOff + stage * L::kAStage;
+                        if (wide & 2) {
+                            tma_load_3d(a_s, &P->tmap_a, 0, ks * kBK, it.m_tile * (kBM / 64), full);
+                        } else {
+                            for (int c = 0; c < kBM / 64; ++c)
+                                tma_load_3d(a_s + c * L::kChunk, &P->tmap_a, it.m_tile * kBM + 64 * c, ks * kBK, 0, full);
+                        }
+                    }
+                    const uint32_t b_s = sbase + L::kBOff + stage * L::kBStage;
+                    if (wide & 1) {
+                        tma_load_3d(b_s, &P->tmap_b, 0, ks * kBK, n0 >> 6, full);
+                    } else {
+                        for (int c = 0; c < chunks; ++c) tma_load_3d(b_s + c * L::kChunk, &P->tmap_b, n0 + 64 * c, ks * kBK, 0, full);
+                    }
+                    if (++stage == BSTAGES) { stage = 0; phase ^= 1u; }
+                    if ((ks & 7) == 7) publish(n + 1 + kPublishAhead, false);
+                }
             }
+            // every CTA takes exactly one item past the end of the list; the CTA that does so last resets the queue
             if (gp.dynamic) {
                 __threadfence();
                 const int done = atomicAdd(gp.queue + 1, 1);
-                if (done == (int)gridDim.x - 1) {            // every CTA has taken its last item: ready for the next launch
+                if (done == (int)gridDim.x - 1) {
                     gp.queue[0] = 0;
                     gp.queue[1] = 0;
                     __threadfence();
                 }
             }
         }
-    } else if (warp == 0) {
-        // ------------------------------------------------------------------ TMA producer of B
-        if (lane == 0) {
-            uint32_t stage = 0, phase = 0;
-            int last_prob = -1;
-            bool ok = true;
-            Item it;
-            for (uint32_t n = 0; ok && take_item(n, it, false); ++n) {
-                const Problem* P = problem_of(it.prob);
-                if (gp.probs && it.prob != last_prob) {
-                    fence_tensormap_acquire(&P->tmap_b);
-                    last_prob = it.prob;
-                }
-                const int n0 = it.n_tile * BN;
-                const int chunks = min(BN / 64, (P->N - n0 + 63) >> 6);
-                for (int ks = it.ks0; ks < it.ks1; ++ks) {
-                    if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, kStatusWaitFused)) { ok = false; break; }
-                    const uint32_t full = bar_full + 8 * stage;
-                    mbar_arrive_expect_tx(full, (uint32_t)chunks * L::kChunk);
-                    const uint32_t b_s = sbase + L::kBOff + stage * L::kBStage;
-                    for (int c = 0; c < chunks; ++c) tma_load_3d(b_s + c * L::kChunk, &P->tmap_b, n0 + 64 * c, ks * kBK, 0, full);
-                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
-                }
-            }
-        }
-    } else if (warp == 1) {
+      } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
         uint32_t stage = 0, phase = 0, acc_it = 0;
         bool ok = true;
@@ -292,7 +351,8 @@ sspmm_fused_kernel(const __grid_constant__ Params gp) {
             tc_fence_after_sync();
             const uint32_t d_tmem = tmem_base + buf * BN;
             for (int ks = it.ks0; ks < it.ks1; ++ks) {
-                if (!__all_sync(0xffffffffu, mbar_wait(bar_full + 8 * stage, phase, abort_flag, kStatusWaitFused))) { ok = false; break; }
+                if (!__all_sync(0xffffffffu, (ATMA || mbar_wait(bar_a_full + 8 * stage, phase, abort_flag, kStatusWaitFused)) &&
+                                            mbar_wait(bar_b_full + 8 * stage, phase, abort_flag, kStatusWaitFused))) { ok = false; break; }
                 tc_fence_after_sync();
                 if (lane == 0) {
                     const uint32_t a_s = sbase + L::kAOff + stage * L::kAStage;
@@ -315,57 +375,125 @@ sspmm_fused_kernel(const __grid_constant__ Params gp) {
             __syncwarp();
             ++acc_it;
         }
-    } else if (warp >= 8) {
+      }
+    } else if (warp >= kLoaderWarp0) {
+      if constexpr (!ATMA) {
         // ------------------------------------------------------------------ A loaders
-        const int group = (warp - 8) >> 2;
-        const int t = threadIdx.x - (256 + kGroupThreads * group);
-        uint32_t it_count = 0;
-        bool ok = true;
+        // The groups take the stages of the CTA's stage sequence in turn.  A stage goes through three steps,
+        // each of which waits for memory: metadata, value vectors, shared-memory slot.  Under load a request
+        // to L2 is under way for well over a thousand cycles, longer than the group's turn comes round, so a
+        // thread keeps four of its stages in flight (two with metadata requested, two with value vectors
+        // requested) and runs ahead across item boundaries: the latencies overlap instead of adding up.
+        const int group = (warp - kLoaderWarp0) >> 2;
+        const int t = threadIdx.x - (kLoaderWarp0 * 32 + kGroupThreads * group);
+        uint32_t n_item = 0, it_count = 0;
+        uint32_t c_finish = (uint32_t)group;    // this group's stages are group, group + kLoaderGroups, ... in order
+        int s_next = 0, steps = 0, item_v = 0;
+        bool have_item = false, done = false;
         Item it;
-        for (uint32_t n = 0; ok && take_item(n, it, true); ++n) {
-            const Problem* P = problem_of(it.prob);
-            const int steps = it.ks1 - it.ks0;
-            // first step of this item that belongs to this group (groups alternate over the CTA's stage sequence)
-            int s = ((int)(it_count & 1u) == group) ? 0 : 1;
-            if (P->V == 16) {
-                uint4 meta = s < steps ? AStage<16>::load_meta(P, it.m_tile, it.ks0 + s, t) : make_uint4(0, 0, 0, 0);
-                for (; s < steps; s += kLoaderGroups) {
-                    const uint32_t c = it_count + (uint32_t)s;
-                    const uint32_t stage = c % STAGES, phase = (c / STAGES) & 1u;
-                    AStage<16> a;
-                    a.load(P, meta, t);
-                    if (s + kLoaderGroups < steps) meta = AStage<16>::load_meta(P, it.m_tile, it.ks0 + s + kLoaderGroups, t);
-                    if (!__all_sync(0xffffffffu, mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, kStatusWaitFused))) { ok = false; break; }
-                    a.store(smem + L::kAOff + stage * L::kAStage, t);
-                    fence_proxy_async_smem();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(bar_full + 8 * stage);
+        const __half* item_values = nullptr;
+        const uint4* item_meta = nullptr;       // this thread's metadata word of the item's first stage
+        int meta_stride = 0;                    // uint4 words between consecutive K steps
+        // next stage of this group; meta_at = where its metadata for this thread lives
+        auto next_stage = [&](const uint4*& meta_at) -> StageDesc {
+            StageDesc d;
+            d.values = nullptr; d.V = 0;
+            for (;;) {
+                if (done) return d;
+                if (!have_item) {
+                    if (!take_item(n_item, it, true)) { done = true; return d; }
+                    ++n_item;
+                    have_item = true;
+                    const Problem* P = problem_of(it.prob);
+                    steps = it.ks1 - it.ks0;
+                    s_next = (group + kLoaderGroups - (int)(it_count % kLoaderGroups)) % kLoaderGroups;
+                    const int V = P->V;
+                    item_values = P->values;
+                    if (P->posmap) {
+                        // kGroupThreads threads x (4 or 8) ints per stage: one or two 16-byte words per thread
+                        item_v = V + 32;
+                        meta_stride = kGroupThreads * (V == 16 ? 1 : 2);
+                        item_meta = reinterpret_cast<const uint4*>(P->posmap) +
+                                    ((int64_t)it.m_tile * P->k_steps + it.ks0) * meta_stride + t * (V == 16 ? 1 : 2);
+                    } else {
+                        item_v = V;
+                        meta_stride = kBM / V;
+                        item_meta = P->meta + ((int64_t)it.m_tile * P->k_steps + it.ks0) * meta_stride + t / (kGroupThreads / meta_stride);
+                    }
                 }
-            } else {
-                uint4 meta = s < steps ? AStage<8>::load_meta(P, it.m_tile, it.ks0 + s, t) : make_uint4(0, 0, 0, 0);
-                for (; s < steps; s += kLoaderGroups) {
-                    const uint32_t c = it_count + (uint32_t)s;
-                    const uint32_t stage = c % STAGES, phase = (c / STAGES) & 1u;
-                    AStage<8> a;
-                    a.load(P, meta, t);
-                    if (s + kLoaderGroups < steps) meta = AStage<8>::load_meta(P, it.m_tile, it.ks0 + s + kLoaderGroups, t);
-                    if (!__all_sync(0xffffffffu, mbar_wait(bar_empty + 8 * stage, phase ^ 1u, abort_flag, kStatusWaitFused))) { ok = false; break; }
-                    a.store(smem + L::kAOff + stage * L::kAStage, t);
-                    fence_proxy_async_smem();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(bar_full + 8 * stage);
+                if (s_next < steps) {
+                    d.values = item_values; d.V = item_v;
+                    meta_at = item_meta + (int64_t)s_next * meta_stride;
+                    s_next += kLoaderGroups;
+                    return d;
                 }
+                it_count += (uint32_t)steps;
+                have_item = false;
             }
-            it_count += (uint32_t)steps;
+        };
+        // metadata words of a stage: one (masks; positions at V = 16) or two (positions at V = 8)
+        auto load_meta = [&](const StageDesc& d, const uint4* meta_at, uint4 (&m)[2]) {
+            m[0] = __ldg(meta_at);
+            if (d.V == 32 + 8) m[1] = __ldg(meta_at + 1);
+        };
+        // requests the value vectors of a stage whose metadata has arrived
+        auto load = [&](const StageDesc& d, const uint4 (&m)[2], uint4 (&v)[8]) {
+            int jj[8];
+            if (d.V == 16) { ATile<16>::positions(m[0], t, jj); ATile<16>::load(d.values, jj, v); }
+            else if (d.V == 8) { ATile<8>::positions(m[0], t, jj); ATile<8>::load(d.values, jj, v); }
+            else if (d.V == 32 + 16) {
+                jj[0] = (int)m[0].x; jj[1] = (int)m[0].y; jj[2] = (int)m[0].z; jj[3] = (int)m[0].w;
+                ATile<16>::load(d.values, jj, v);
+            } else {
+                jj[0] = (int)m[0].x; jj[1] = (int)m[0].y; jj[2] = (int)m[0].z; jj[3] = (int)m[0].w;
+                jj[4] = (int)m[1].x; jj[5] = (int)m[1].y; jj[6] = (int)m[1].z; jj[7] = (int)m[1].w;
+                ATile<8>::load(d.values, jj, v);
+            }
+        };
+        // the group's next stage in order: waits for its slot, stores the tile, hands it to the MMA
+        auto finish = [&](const StageDesc& d, const uint4 (&v)[8]) -> bool {
+            const uint32_t stage = c_finish % kAStages, phase = (c_finish / kAStages) & 1u;
+            c_finish += kLoaderGroups;
+            if (!__all_sync(0xffffffffu, mbar_wait(bar_a_empty + 8 * stage, phase ^ 1u, abort_flag, kStatusWaitFused))) return false;
+            uint8_t* a_s = smem + L::kAOff + stage * L::kAStage;
+            if ((d.V & 31) == 16) ATile<16>::store(a_s, t, v); else ATile<8>::store(a_s, t, v);
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_a_full + 8 * stage);
+            return true;
+        };
+        uint4 v0[8], v1[8], m0[2], m1[2];
+        const uint4* meta_at = nullptr;
+        // invariant at the top of the loop: v0 / v1 = value vectors of d0 / d1 (requested), m0 / m1 = metadata of d2 / d3 (requested)
+        StageDesc d0 = next_stage(meta_at);
+        if (d0.V) { load_meta(d0, meta_at, m0); load(d0, m0, v0); }
+        StageDesc d1 = next_stage(meta_at);
+        if (d1.V) { load_meta(d1, meta_at, m1); load(d1, m1, v1); }
+        StageDesc d2 = next_stage(meta_at);
+        if (d2.V) load_meta(d2, meta_at, m0);
+        StageDesc d3 = next_stage(meta_at);
+        if (d3.V) load_meta(d3, meta_at, m1);
+        while (d0.V) {
+            if (!finish(d0, v0)) break;
+            if (d2.V) load(d2, m0, v0);
+            StageDesc d4 = next_stage(meta_at);
+            if (d4.V) load_meta(d4, meta_at, m0);
+            if (!d1.V) break;
+            if (!finish(d1, v1)) break;
+            if (d3.V) load(d3, m1, v1);
+            StageDesc d5 = next_stage(meta_at);
+            if (d5.V) load_meta(d5, meta_at, m1);
+            d0 = d2; d1 = d3; d2 = d4; d3 = d5;
         }
-    } else if (warp >= 4) {
+      }
+    } else {
         // ------------------------------------------------------------------ epilogue
         // Each thread owns one row of the 128-row tile and handles 32 accumulator columns at a time.
         constexpr int kColsPerStore = 64 / (int)sizeof(OutT);          // 32 (fp16) or 16 (fp32)
         constexpr int kStoresPerLoad = 32 / kColsPerStore;
         const int q = warp & 3;
         const int row = q * 32 + lane;
-        const bool issuer = (threadIdx.x == 128);
+        const bool issuer = (threadIdx.x == kEpilogueWarp0 * 32);
         const uint32_t swz = (uint32_t)((row >> 1) & 3);
         uint32_t acc_it = 0, st_it = 0;
         int last_prob = -1;
@@ -517,6 +645,82 @@ sspmm_fused_kernel(const __grid_constant__ Params gp) {
     }
 }
 
+// ---- expansion of the compressed operands of a group ---------------------------------------
+// At[k][i*V .. i*V+V) = value vector of vector row i at column k, or zeros; every element of At is written, so
+// nothing from an earlier run survives.  One CTA per (product, chunk of 1024 columns, row slot): the row's column
+// list becomes a column -> vector map in shared memory, then every column of the chunk is written.
+struct ExpandJob {
+    const int* row_offsets;
+    const int* col;
+    const __half* values;
+    __half* at;
+    int m_vec, K, V, chunks;       // chunks = ceil(K / 1024)
+    int slots;                     // CTAs that share the vector rows of one chunk
+    int unit_base;                 // first unit (CTA) of this job
+};
+constexpr int kExpandChunk = 1024;
+
+template <int V>
+__device__ __forceinline__ void expand_rows(const ExpandJob& job, int chunk, int slot, int* col_to_vec) {
+    const int64_t mp = (int64_t)job.m_vec * V;
+    const int k_begin = chunk * kExpandChunk;
+    const int k_end = min(job.K, k_begin + kExpandChunk);
+    for (int i = slot; i < job.m_vec; i += job.slots) {
+        for (int k = threadIdx.x; k < kExpandChunk; k += blockDim.x) col_to_vec[k] = -1;
+        __syncthreads();
+        const int j0 = job.row_offsets[i], j1 = job.row_offsets[i + 1];
+        for (int j = j0 + threadIdx.x; j < j1; j += 4 * blockDim.x) {      // four independent loads in flight
+            int c[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) c[q] = (j + q * (int)blockDim.x < j1) ? __ldg(job.col + j + q * blockDim.x) : -1;
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+                if (c[q] >= k_begin && c[q] < k_end) col_to_vec[c[q] - k_begin] = j + q * blockDim.x;
+        }
+        __syncthreads();
+        for (int k = k_begin + threadIdx.x; k < k_end; k += 4 * blockDim.x) {
+            int js[4];
+            uint4 v[4][V / 8];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) js[q] = (k + q * (int)blockDim.x < k_end) ? col_to_vec[k + q * blockDim.x - k_begin] : -1;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const uint4* src = reinterpret_cast<const uint4*>(job.values + (int64_t)(js[q] >= 0 ? js[q] : 0) * V);
+#pragma unroll
+                for (int h = 0; h < V / 8; ++h) v[q][h] = js[q] >= 0 ? __ldg(src + h) : make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const int kq = k + q * (int)blockDim.x;
+                if (kq < k_end) {
+                    uint4* dst = reinterpret_cast<uint4*>(job.at + (int64_t)kq * mp + (int64_t)i * V);
+#pragma unroll
+                    for (int h = 0; h < V / 8; ++h) dst[h] = v[q][h];
+                }
+            }
+        }
+        __syncthreads();
+    }
+}
+
+__global__ void __launch_bounds__(256)
+expand_group_kernel(const ExpandJob* __restrict__ jobs, int n_jobs) {
+    __shared__ int col_to_vec[kExpandChunk];
+    __shared__ ExpandJob job;
+    if (threadIdx.x == 0) {
+        int lo = 0, hi = n_jobs - 1;
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (jobs[mid].unit_base <= (int)blockIdx.x) lo = mid; else hi = mid - 1;
+        }
+        job = jobs[lo];
+    }
+    __syncthreads();
+    const int local = (int)blockIdx.x - job.unit_base;
+    const int chunk = local % job.chunks, slot = local / job.chunks;
+    if (job.V == 16) expand_rows<16>(job, chunk, slot, col_to_vec); else expand_rows<8>(job, chunk, slot, col_to_vec);
+}
+
 // ---- plan construction ------------------------------------------------------------------
 // One CTA per vector row: bitmap of the row's columns in shared memory -> masks, starts, permutation.
 // flags: [0] irregular (column outside [0, K) or listed twice in a vector row), [1] some row is not ascending,
@@ -579,6 +783,23 @@ plan_build_kernel(int m_vec, int K, int k_steps, const int* __restrict__ row_off
     if (threadIdx.x == 0) atomicMax(flags + 2, j1 - j0);
 }
 
+// Positions for structures with rows that are not ascending: posmap[((tile * k_steps + ks) * 128 + t) * SLOTS + q] =
+// index of the vector that loader thread t puts into its slot q of that stage, or -1.
+template <int V>
+__global__ void __launch_bounds__(256)
+plan_posmap_kernel(long long slots, const uint4* __restrict__ meta, const int* __restrict__ perm, int* __restrict__ posmap) {
+    using A = ATile<V>;
+    const long long idx = (long long)blockIdx.x * 256 + threadIdx.x;
+    if (idx >= slots) return;
+    const int q = (int)(idx % A::SLOTS);
+    const int t = (int)((idx / A::SLOTS) % kGroupThreads);
+    const long long stage = idx / (A::SLOTS * kGroupThreads);
+    const int kk = t % A::TPR + A::TPR * q;
+    const uint4 m = meta[stage * A::R + t / A::TPR];
+    const unsigned long long mask = (unsigned long long)m.x | ((unsigned long long)m.y << 32);
+    posmap[idx] = ((mask >> kk) & 1ull) ? perm[(int)m.z + __popcll(mask & ((1ull << kk) - 1ull))] : -1;
+}
+
 using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -606,6 +827,18 @@ bool encode_map(EncodeFn enc, CUtensorMap* m, CUtensorMapDataType dt, size_t es,
                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Chunked view of a row-major [rows][width] fp16 matrix (width % 64 == 0): {64, rows, width / 64}; a box
+// {64, 64, chunks} lands as `chunks` consecutive [64 rows][128 B] swizzled blocks, the layout the MMA descriptors expect.
+bool encode_chunked(EncodeFn enc, CUtensorMap* m, const void* base, uint64_t width, uint64_t rows, uint32_t chunks) {
+    const cuuint64_t gdim[3] = {64, rows, width / 64};
+    const cuuint64_t gstride[2] = {width * 2, 128};
+    const cuuint32_t box[3] = {64, 64, chunks};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    return enc(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(base), gdim, gstride, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 }  // namespace fused
 }  // namespace sspmm_b200
 
@@ -621,17 +854,20 @@ struct sspmm_plan {
     bool sorted;
     const int* row_offsets;    // the caller's arrays (not owned)
     const int* column_indices;
-    uint4* meta;               // owned
-    int* perm;                 // owned, null when every row is ascending
+    uint4* meta;               // owned: column masks (every row ascending)
+    int* posmap;               // owned: positions (some row not ascending); exactly one of the two is set when fused
 };
 
 struct sspmm_group {
     int device, count, BN;
     bool out_f16;
+    bool expanded;             // A tiles by TMA from dense transposed copies written by expand_group_kernel at every run
     int n_items, grid;
-    void* dev_block;           // one allocation: problems | items | queue | counters | partials
+    void* dev_block;           // one allocation: problems | items | queue | counters | expansion jobs | partials | copies of A
     fused::Params params;
-    size_t partial_bytes;
+    const fused::ExpandJob* d_jobs;
+    int expand_units;
+    size_t scratch_bytes;      // partial tiles + copies of A
 };
 
 namespace sspmm_b200 {
@@ -641,10 +877,10 @@ constexpr size_t kMaxMetaBytes = (size_t)256 << 20;
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-template <int BN, int STAGES, typename OutT>
+template <int BN, int STAGES, typename OutT, bool ATMA>
 cudaError_t launch_typed(const Params& p, int grid, cudaStream_t st, bool setup_only) {
     using L = Layout<BN, STAGES>;
-    auto kern = sspmm_fused_kernel<BN, STAGES, OutT>;
+    auto kern = sspmm_fused_kernel<BN, STAGES, OutT, ATMA>;
     static DeviceOnce once;
     if (!once.done()) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
@@ -656,10 +892,16 @@ cudaError_t launch_typed(const Params& p, int grid, cudaStream_t st, bool setup_
     return cudaGetLastError();
 }
 
-cudaError_t launch(const Params& p, int BN, bool out_f16, int grid, cudaStream_t st, bool setup_only = false) {
-    if (BN == 256) return out_f16 ? launch_typed<256, 4, __half>(p, grid, st, setup_only) : launch_typed<256, 4, float>(p, grid, st, setup_only);
-    if (BN == 128) return out_f16 ? launch_typed<128, 6, __half>(p, grid, st, setup_only) : launch_typed<128, 6, float>(p, grid, st, setup_only);
-    return out_f16 ? launch_typed<64, 8, __half>(p, grid, st, setup_only) : launch_typed<64, 8, float>(p, grid, st, setup_only);
+template <typename OutT, bool ATMA>
+cudaError_t launch_bn(const Params& p, int BN, int grid, cudaStream_t st, bool setup_only) {
+    if (BN == 256) return launch_typed<256, 4, OutT, ATMA>(p, grid, st, setup_only);
+    if (BN == 128) return launch_typed<128, 6, OutT, ATMA>(p, grid, st, setup_only);
+    return launch_typed<64, 8, OutT, ATMA>(p, grid, st, setup_only);
+}
+
+cudaError_t launch(const Params& p, int BN, bool out_f16, bool a_tma, int grid, cudaStream_t st, bool setup_only = false) {
+    if (a_tma) return out_f16 ? launch_bn<__half, true>(p, BN, grid, st, setup_only) : launch_bn<float, true>(p, BN, grid, st, setup_only);
+    return out_f16 ? launch_bn<__half, false>(p, BN, grid, st, setup_only) : launch_bn<float, false>(p, BN, grid, st, setup_only);
 }
 
 // Fills everything of a Problem but nothing that lives on the device.  Returns false with the error set.
@@ -674,17 +916,18 @@ bool fill_problem(Problem* P, const sspmm_plan* plan, const void* values, const 
     }
     const int Mp = plan->m_vec * plan->V;
     const size_t oes = out_f16 ? 2 : 4;
-    if (!encode_map(enc, &P->tmap_b, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, rhs, (uint64_t)N, (uint64_t)plan->K, 64, 64,
-                    CU_TENSOR_MAP_SWIZZLE_128B) ||
+    P->wide = (N % 64 == 0 && encode_chunked(enc, &P->tmap_b, rhs, (uint64_t)N, (uint64_t)plan->K, (uint32_t)(BN / 64))) ? 1 : 0;
+    if ((!P->wide && !encode_map(enc, &P->tmap_b, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, rhs, (uint64_t)N, (uint64_t)plan->K, 64, 64,
+                                 CU_TENSOR_MAP_SWIZZLE_128B)) ||
         !encode_map(enc, &P->tmap_c, out_f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, oes, out,
                     (uint64_t)N, (uint64_t)Mp, (uint32_t)(64 / oes), 128, CU_TENSOR_MAP_SWIZZLE_64B)) {
         set_error("cuTensorMapEncodeTiled failed (Mp=%d N=%d K=%d)", Mp, N, plan->K);
         return false;
     }
-    P->meta = plan->meta; P->perm = plan->perm;
+    P->meta = plan->meta; P->posmap = plan->posmap;
     P->values = static_cast<const __half*>(values); P->out = out;
     P->Mp = Mp; P->N = N; P->K = plan->K; P->V = plan->V;
-    P->k_steps = plan->k_steps; P->m_tiles = plan->m_tiles; P->n_tiles = (N + BN - 1) / BN; P->reserved = 0;
+    P->k_steps = plan->k_steps; P->m_tiles = plan->m_tiles; P->n_tiles = (N + BN - 1) / BN;
     return true;
 }
 
@@ -713,11 +956,13 @@ int sspmm_plan_create(int m_vec, int vec_length, int K, const int* d_row_offsets
     pl->row_offsets = d_row_offsets; pl->column_indices = d_column_indices;
     pl->m_tiles = (m_vec * vec_length + fused::kBM - 1) / fused::kBM;
     pl->k_steps = (K + fused::kBK - 1) / fused::kBK;
-    pl->nvec = 0; pl->max_len = 0; pl->fused = false; pl->sorted = true; pl->meta = nullptr; pl->perm = nullptr;
+    pl->nvec = 0; pl->max_len = 0; pl->fused = false; pl->sorted = true; pl->meta = nullptr; pl->posmap = nullptr;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int* perm = nullptr;       // position in column order -> index of the vector; only needed to build posmap
     auto failed = [&](cudaError_t e, const char* what) {
         if (pl->meta) cudaFree(pl->meta);
-        if (pl->perm) cudaFree(pl->perm);
+        if (pl->posmap) cudaFree(pl->posmap);
+        if (perm) cudaFree(perm);
         delete pl;
         set_error("%s: %s", what, cudaGetErrorString(e));
         return (int)e;
@@ -740,7 +985,7 @@ int sspmm_plan_create(int m_vec, int vec_length, int K, const int* d_row_offsets
     }
     int* flags = nullptr;
     e = cudaMalloc(&pl->meta, meta_bytes);
-    if (e == cudaSuccess) e = cudaMalloc(&pl->perm, (size_t)nvec * sizeof(int));
+    if (e == cudaSuccess) e = cudaMalloc(&perm, (size_t)nvec * sizeof(int));
     if (e == cudaSuccess) e = cudaMalloc(&flags, 4 * sizeof(int));
     if (e == cudaSuccess) e = cudaMemsetAsync(pl->meta, 0, meta_bytes, st);
     if (e == cudaSuccess) e = cudaMemsetAsync(flags, 0, 4 * sizeof(int), st);
@@ -749,7 +994,7 @@ int sspmm_plan_create(int m_vec, int vec_length, int K, const int* d_row_offsets
         auto kern = vec_length == 16 ? fused::plan_build_kernel<16> : fused::plan_build_kernel<8>;
         if (smem > 48 * 1024) e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e == cudaSuccess) {
-            kern<<<m_vec, 256, smem, st>>>(m_vec, K, pl->k_steps, d_row_offsets, d_column_indices, pl->meta, pl->perm, flags);
+            kern<<<m_vec, 256, smem, st>>>(m_vec, K, pl->k_steps, d_row_offsets, d_column_indices, pl->meta, perm, flags);
             e = cudaGetLastError();
         }
     }
@@ -761,8 +1006,27 @@ int sspmm_plan_create(int m_vec, int vec_length, int K, const int* d_row_offsets
     pl->fused = h[0] == 0;
     pl->sorted = h[1] == 0;
     pl->max_len = h[2];
-    if (pl->sorted || !pl->fused) { cudaFree(pl->perm); pl->perm = nullptr; }
-    if (!pl->fused) { cudaFree(pl->meta); pl->meta = nullptr; }
+    if (pl->fused && !pl->sorted) {
+        // some row is not ascending: replace the masks by explicit positions
+        const int slots_per_thread = vec_length == 16 ? 4 : 8;
+        const long long slots = (long long)pl->m_tiles * pl->k_steps * fused::kGroupThreads * slots_per_thread;
+        if ((size_t)slots * sizeof(int) > fused::kMaxMetaBytes) {
+            pl->fused = false;
+        } else {
+            e = cudaMalloc(&pl->posmap, (size_t)slots * sizeof(int));
+            if (e == cudaSuccess) {
+                const unsigned blocks = (unsigned)((slots + 255) / 256);
+                if (vec_length == 16) fused::plan_posmap_kernel<16><<<blocks, 256, 0, st>>>(slots, pl->meta, perm, pl->posmap);
+                else fused::plan_posmap_kernel<8><<<blocks, 256, 0, st>>>(slots, pl->meta, perm, pl->posmap);
+                e = cudaGetLastError();
+            }
+            if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+            if (e != cudaSuccess) return failed(e, "building the plan's position table");
+        }
+    }
+    cudaFree(perm);
+    perm = nullptr;
+    if (!pl->fused || pl->posmap) { cudaFree(pl->meta); pl->meta = nullptr; }
     *plan = pl;
     return 0;
 }
@@ -770,7 +1034,7 @@ int sspmm_plan_create(int m_vec, int vec_length, int K, const int* d_row_offsets
 int sspmm_plan_destroy(sspmm_plan* plan) {
     if (!plan) return 0;
     if (plan->meta) cudaFree(plan->meta);
-    if (plan->perm) cudaFree(plan->perm);
+    if (plan->posmap) cudaFree(plan->posmap);
     delete plan;
     return 0;
 }
@@ -782,7 +1046,8 @@ int sspmm_plan_info(const sspmm_plan* plan, int64_t* nvec, int* one_launch, int*
     if (ascending) *ascending = plan->sorted ? 1 : 0;
     if (device_bytes) {
         const int R = fused::kBM / plan->V;
-        *device_bytes = (plan->meta ? (int64_t)plan->m_tiles * plan->k_steps * R * 16 : 0) + (plan->perm ? plan->nvec * 4 : 0);
+        *device_bytes = plan->meta ? (int64_t)plan->m_tiles * plan->k_steps * R * 16
+                                   : (plan->posmap ? (int64_t)plan->m_tiles * plan->k_steps * fused::kGroupThreads * (plan->V == 16 ? 4 : 8) * 4 : 0);
     }
     return 0;
 }
@@ -814,16 +1079,17 @@ int sspmm_planned(const sspmm_plan* plan, const void* values_f16, const void* rh
     p.n_items = (int)tiles;
     const int rounds = (int)((tiles + sms - 1) / sms);
     const int grid = (int)((tiles + rounds - 1) / rounds);
-    cudaError_t e = fused::launch(p, BN, out_is_f16 != 0, grid, static_cast<cudaStream_t>(stream));
+    cudaError_t e = fused::launch(p, BN, out_is_f16 != 0, false, grid, static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) { set_error("SpMM launch: %s", cudaGetErrorString(e)); return (int)e; }
     return 0;
 }
 
-int sspmm_group_create(const sspmm_group_item* items, int count, int out_is_f16, sspmm_group** group) {
+int sspmm_group_create(const sspmm_group_item* items, int count, int out_is_f16, int mode, sspmm_group** group) {
     set_error("%s", "");
     if (!group) { set_error("null output pointer"); return (int)cudaErrorInvalidValue; }
     *group = nullptr;
     if (!items || count <= 0) { set_error("a group needs at least one product"); return (int)cudaErrorInvalidValue; }
+    if (mode < 0 || mode > 2) { set_error("group mode must be 0 (automatic), 1 (compressed) or 2 (expanded)"); return (int)cudaErrorInvalidValue; }
     const int sms = current_device_sm_count();
     if (sms <= 0) return (int)cudaErrorNoDevice;
     int dev = 0;
@@ -893,19 +1159,67 @@ int sspmm_group_create(const sspmm_group_item* items, int count, int out_is_f16,
     g->device = dev; g->count = count; g->BN = BN; g->out_f16 = out_is_f16 != 0;
     g->n_items = (int)list.size();
     g->grid = g->n_items < sms ? g->n_items : sms;
+    // Measured on B200: with the A tiles built by the loader warps a K step takes about 1150 cycles, with A tiles
+    // fetched by TMA from a dense copy about 700-750; writing the copies costs one more launch and a few tens of
+    // microseconds.  So groups with much work per SM expand, small ones (latency matters) do not.
+    g->expanded = mode == 2 || (mode == 0 && per_sm >= 48.0);
     auto up = [](size_t x) { return (x + 255) & ~(size_t)255; };
+    std::vector<fused::ExpandJob> jobs;
+    std::vector<size_t> at_off((size_t)count, 0);
+    size_t at_bytes = 0;
+    g->expand_units = 0;
+    if (g->expanded) {
+        jobs.resize((size_t)count);
+        for (int i = 0; i < count; ++i) {
+            const sspmm_plan* pl = items[i].plan;
+            at_off[i] = at_bytes;
+            at_bytes += up((size_t)pl->K * pl->m_vec * pl->V * sizeof(__half));
+            fused::ExpandJob& j = jobs[i];
+            j.row_offsets = pl->row_offsets; j.col = pl->column_indices;
+            j.values = static_cast<const __half*>(items[i].values_f16); j.at = nullptr;
+            j.m_vec = pl->m_vec; j.K = pl->K; j.V = pl->V;
+            j.chunks = (pl->K + fused::kExpandChunk - 1) / fused::kExpandChunk;
+            j.slots = pl->m_vec < 2048 ? pl->m_vec : 2048;       // one vector row per CTA: the kernel is a chain of dependent reads
+            j.unit_base = g->expand_units;
+            g->expand_units += j.chunks * j.slots;
+        }
+    }
     const size_t off_items = up(probs.size() * sizeof(fused::Problem));
     const size_t off_queue = off_items + up(list.size() * sizeof(fused::Item));
     const size_t off_counters = off_queue + 256;
-    const size_t off_partials = off_counters + up((size_t)(cslots + 1) * sizeof(int));
-    g->partial_bytes = (size_t)pslots * fused::kBM * BN * sizeof(float);
-    const size_t total = off_partials + g->partial_bytes;
+    const size_t off_jobs = off_counters + up((size_t)(cslots + 1) * sizeof(int));
+    const size_t off_partials = off_jobs + up(jobs.size() * sizeof(fused::ExpandJob));
+    const size_t partial_bytes = up((size_t)pslots * fused::kBM * BN * sizeof(float));
+    const size_t off_at = off_partials + partial_bytes;
+    g->scratch_bytes = partial_bytes + at_bytes;
+    const size_t total = off_at + at_bytes;
     cudaError_t e = cudaMalloc(&g->dev_block, total);
     if (e == cudaSuccess) e = cudaMemset(g->dev_block, 0, off_partials);
     uint8_t* base = static_cast<uint8_t*>(g->dev_block);
+    bool maps_ok = true;
+    if (e == cudaSuccess && g->expanded) {
+        fused::EncodeFn enc = fused::encode_fn();
+        for (int i = 0; i < count && maps_ok; ++i) {
+            jobs[i].at = reinterpret_cast<__half*>(base + off_at + at_off[i]);
+            if (enc && probs[i].Mp % 64 == 0 &&
+                fused::encode_chunked(enc, &probs[i].tmap_a, jobs[i].at, (uint64_t)probs[i].Mp, (uint64_t)probs[i].K, fused::kBM / 64)) {
+                probs[i].wide |= 2;
+                continue;
+            }
+            maps_ok = enc && fused::encode_map(enc, &probs[i].tmap_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, jobs[i].at,
+                                               (uint64_t)probs[i].Mp, (uint64_t)probs[i].K, 64, 64, CU_TENSOR_MAP_SWIZZLE_128B);
+        }
+        if (maps_ok) e = cudaMemcpy(base + off_jobs, jobs.data(), jobs.size() * sizeof(fused::ExpandJob), cudaMemcpyHostToDevice);
+    }
     if (e == cudaSuccess) e = cudaMemcpy(base, probs.data(), probs.size() * sizeof(fused::Problem), cudaMemcpyHostToDevice);
     if (e == cudaSuccess) e = cudaMemcpy(base + off_items, list.data(), list.size() * sizeof(fused::Item), cudaMemcpyHostToDevice);
-    if (e == cudaSuccess) e = fused::launch(g->params, BN, g->out_f16, 1, nullptr, true);
+    if (e == cudaSuccess) e = fused::launch(g->params, BN, g->out_f16, g->expanded, 1, nullptr, true);
+    if (e == cudaSuccess && !maps_ok) {
+        cudaFree(g->dev_block);
+        delete g;
+        set_error("cuTensorMapEncodeTiled failed for a dense copy of A");
+        return (int)cudaErrorInvalidValue;
+    }
     if (e != cudaSuccess) {
         if (g->dev_block) cudaFree(g->dev_block);
         delete g;
@@ -919,6 +1233,7 @@ int sspmm_group_create(const sspmm_group_item* items, int count, int out_is_f16,
     g->params.queue = reinterpret_cast<int*>(base + off_queue);
     g->params.counters = reinterpret_cast<int*>(base + off_counters);
     g->params.partials = reinterpret_cast<float*>(base + off_partials);
+    g->d_jobs = reinterpret_cast<const fused::ExpandJob*>(base + off_jobs);
     *group = g;
     return 0;
 }
@@ -926,17 +1241,25 @@ int sspmm_group_create(const sspmm_group_item* items, int count, int out_is_f16,
 int sspmm_group_run(sspmm_group* group, void* stream) {
     set_error("%s", "");
     if (!group) { set_error("null group"); return (int)cudaErrorInvalidValue; }
-    cudaError_t e = fused::launch(group->params, group->BN, group->out_f16, group->grid, static_cast<cudaStream_t>(stream));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (group->expanded) {
+        fused::expand_group_kernel<<<group->expand_units, 256, 0, st>>>(group->d_jobs, group->count);
+        cudaError_t e0 = cudaGetLastError();
+        if (e0 != cudaSuccess) { set_error("group expansion launch: %s", cudaGetErrorString(e0)); return (int)e0; }
+    }
+    cudaError_t e = fused::launch(group->params, group->BN, group->out_f16, group->expanded, group->grid, st);
     if (e != cudaSuccess) { set_error("group launch: %s", cudaGetErrorString(e)); return (int)e; }
     return 0;
 }
 
-int sspmm_group_info(const sspmm_group* group, int* tile_columns, int* work_items, int* ctas, int64_t* device_bytes) {
+int sspmm_group_info(const sspmm_group* group, int* tile_columns, int* work_items, int* ctas, int* launches,
+                     int64_t* scratch_bytes) {
     if (!group) return (int)cudaErrorInvalidValue;
     if (tile_columns) *tile_columns = group->BN;
     if (work_items) *work_items = group->n_items;
     if (ctas) *ctas = group->grid;
-    if (device_bytes) *device_bytes = (int64_t)group->partial_bytes;
+    if (launches) *launches = group->expanded ? 2 : 1;
+    if (scratch_bytes) *scratch_bytes = (int64_t)group->scratch_bytes;
     return 0;
 }
 

@@ -908,6 +908,84 @@ cudaError_t svc_emit(const SvcProblem& p, const SvcScratch& s, const long long* 
 }
 
 
+// ---- batches -------------------------------------------------------------------------------
+namespace {
+// index of the matrix that owns position x, for a table whose `base` member is ascending
+template <class F>
+__device__ __forceinline__ int owner_of(long long x, int count, F base_of) {
+    int lo = 0, hi = count - 1;
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (base_of(mid) <= x) lo = mid; else hi = mid - 1;
+    }
+    return lo;
+}
+
+__global__ void __launch_bounds__(256)
+svc_stack_kernel(const SvcBatchEntry* __restrict__ tab, int count, long long rows, long long entries, int* __restrict__ row_ptr,
+                 int* __restrict__ col_idx, __half* __restrict__ vals) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    const long long t0 = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    for (long long r = t0; r <= rows; r += stride) {
+        if (r == rows) { row_ptr[r] = (int)entries; continue; }
+        const int m = owner_of(r, count, [&](int k) { return tab[k].row_base; });
+        const long long lr = r - tab[m].row_base;
+        row_ptr[r] = (int)(tab[m].nnz_base + (lr < tab[m].M ? tab[m].row_ptr[lr] : tab[m].nnz));
+    }
+    for (long long e = t0; e < entries; e += stride) {
+        const int m = owner_of(e, count, [&](int k) { return tab[k].nnz_base; });
+        const long long le = e - tab[m].nnz_base;
+        col_idx[e] = tab[m].col_idx[le];
+        if (vals) vals[e] = tab[m].vals[le];
+    }
+}
+
+__global__ void svc_batch_cuts_kernel(const SvcBatchEntry* __restrict__ tab, int count, const int* __restrict__ vec_ptr,
+                                      long long* __restrict__ cuts) {
+    const int m = blockIdx.x * blockDim.x + threadIdx.x;
+    if (m <= count) cuts[m] = vec_ptr[tab[m].vec_row_base];
+}
+
+__global__ void __launch_bounds__(256)
+svc_batch_row_ptrs_kernel(const SvcBatchEntry* __restrict__ tab, int count, long long vec_rows, const int* __restrict__ vec_ptr,
+                          const long long* __restrict__ cuts, int* __restrict__ out) {
+    // output position x = (stacked vector row) + (matrix index): each matrix has one pointer more than vector rows
+    const long long total = vec_rows + count;
+    for (long long x = (long long)blockIdx.x * blockDim.x + threadIdx.x; x < total; x += (long long)gridDim.x * blockDim.x) {
+        const int m = owner_of(x, count, [&](int k) { return tab[k].vec_row_base + k; });
+        const long long lv = x - tab[m].vec_row_base - m;
+        out[x] = (int)(vec_ptr[tab[m].vec_row_base + lv] - cuts[m]);
+    }
+}
+}  // namespace
+
+cudaError_t svc_stack(const SvcBatchEntry* tab, int count, long long rows, long long entries, int V, int* row_ptr,
+                      int* col_idx, __half* vals, cudaStream_t stream) {
+    (void)V;
+    const long long work = (rows + 1 > entries ? rows + 1 : entries);
+    long long blocks = (work + 255) / 256;
+    const long long cap = (long long)device_sm_count() * 16;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    svc_stack_kernel<<<(int)blocks, 256, 0, stream>>>(tab, count, rows, entries, row_ptr, col_idx, vals);
+    return cudaGetLastError();
+}
+
+cudaError_t svc_batch_cuts(const SvcBatchEntry* tab, int count, const int* vec_ptr, long long* cuts, cudaStream_t stream) {
+    svc_batch_cuts_kernel<<<(count + 1 + 255) / 256, 256, 0, stream>>>(tab, count, vec_ptr, cuts);
+    return cudaGetLastError();
+}
+
+cudaError_t svc_batch_row_ptrs(const SvcBatchEntry* tab, int count, long long vec_rows, const int* vec_ptr,
+                               const long long* cuts, int* out, cudaStream_t stream) {
+    long long blocks = (vec_rows + count + 255) / 256;
+    const long long cap = (long long)device_sm_count() * 16;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    svc_batch_row_ptrs_kernel<<<(int)blocks, 256, 0, stream>>>(tab, count, vec_rows, vec_ptr, cuts, out);
+    return cudaGetLastError();
+}
+
 cudaError_t svc_read_and_clear_bad_column_flag(int* flag, cudaStream_t stream) {
     cudaError_t e = cudaMemcpyFromSymbolAsync(flag, g_svc_bad_column, sizeof(int), 0, cudaMemcpyDeviceToHost, stream);
     if (e != cudaSuccess) return e;

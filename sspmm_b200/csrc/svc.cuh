@@ -41,6 +41,28 @@ cudaError_t svc_count_and_scan(const SvcProblem& p, const SvcScratch& s, bool wi
 cudaError_t svc_emit(const SvcProblem& p, const SvcScratch& s, const long long* class_groups, int* out_col,
                      __half* out_vals, cudaStream_t stream);
 
+// ---- batches: several independent matrices compressed as one stacked matrix ----------------
+// Vector rows are independent of one another and their column order does not depend on K, so a batch
+// is stacked into one tall CSR (each matrix padded with empty rows to a multiple of V rows, so that
+// no vector row straddles two matrices) and compressed in one pass.
+struct SvcBatchEntry {
+    const int* row_ptr;
+    const int* col_idx;
+    const __half* vals;
+    long long row_base;      // first stacked row (a multiple of V)
+    long long nnz_base;      // first stacked entry
+    long long vec_row_base;  // first stacked vector row
+    int M, nnz;
+};
+// tab has count + 1 entries (the last one carries the totals).  Builds the stacked CSR.
+cudaError_t svc_stack(const SvcBatchEntry* tab, int count, long long rows, long long entries, int V, int* row_ptr,
+                      int* col_idx, __half* vals, cudaStream_t stream);
+// cuts[m] = vec_ptr[first vector row of matrix m] for m in 0..count.
+cudaError_t svc_batch_cuts(const SvcBatchEntry* tab, int count, const int* vec_ptr, long long* cuts, cudaStream_t stream);
+// out: for every matrix its m_vec + 1 row pointers, rebased to 0, matrices one after another.
+cudaError_t svc_batch_row_ptrs(const SvcBatchEntry* tab, int count, long long vec_rows, const int* vec_ptr,
+                               const long long* cuts, int* out, cudaStream_t stream);
+
 // Device flag set when a column id outside [0, K) was met (such entries are skipped).
 cudaError_t svc_read_and_clear_bad_column_flag(int* flag, cudaStream_t stream);
 

@@ -97,50 +97,58 @@ def svc(row_ptr: torch.Tensor, col_idx: torch.Tensor, values: Optional[torch.Ten
     return vec_ptr, vec_col, vec_val, replayed.value
 
 
-def svc_batch(mats, vec_length: int):
-    """Sparse vector compression of several independent CSR matrices in one pass.
+def svc_batch(mats, vec_length: int, nnz=None):
+    """Sparse vector compression of several independent CSR matrices in one pass (``svc_batch_begin`` /
+    ``svc_batch_finish``): the matrices are stacked on the device and compressed together.
 
-    ``mats`` is a list of (row_ptr, col_idx, values_or_None, M, K) with device tensors.  Vector rows
-    are independent of one another and their column order does not depend on K, so the matrices are
-    stacked into one tall CSR (each padded with empty rows to a multiple of ``vec_length`` rows, so
-    that no vector row straddles two matrices), compressed once, and the result is cut back into
-    per-matrix pieces.  Returns a list of (vec_row_ptr, vec_col, vec_values_or_None) per matrix and
-    the total number of replayed vector rows.  Throughput path for sweeps of many small matrices."""
+    ``mats`` is a list of (row_ptr, col_idx, values_or_None, M, K) with device tensors; ``nnz`` the list of
+    their non-zero counts (taken from ``col_idx.numel()`` when omitted).  Returns a list of
+    (vec_row_ptr, vec_col, vec_values_or_None) per matrix -- views into three buffers that hold all matrices
+    one after another -- and the total number of replayed vector rows."""
+    import ctypes as C
     if not mats:
         return [], 0
     V = vec_length
+    n = len(mats)
     dev = mats[0][0].device
     with_vals = all(m[2] is not None for m in mats)
-    ptr_parts, bases, m_vecs = [], [], []
-    nnz_base, row_base = 0, 0
+    if nnz is None:
+        nnz = [int(m[1].numel()) for m in mats]
     for (rp, ci, va, M, K) in mats:
         _require(rp, torch.int32, "row_ptr")
-        m_vec = (M + V - 1) // V
-        pad = m_vec * V - M
-        body = rp[:M].to(torch.int64) + nnz_base
-        nnz = int(rp[M].item()) if M > 0 else 0
-        tail = torch.full((pad,), nnz_base + nnz, dtype=torch.int64, device=dev)
-        ptr_parts += [body, tail]
-        bases.append((row_base // V, nnz_base))
-        m_vecs.append(m_vec)
-        nnz_base += nnz
-        row_base += m_vec * V
-    ptr_parts.append(torch.tensor([nnz_base], dtype=torch.int64, device=dev))
-    if nnz_base >= 2 ** 31:
-        raise ValueError("stacked matrix does not fit 32-bit indices")
-    row_ptr = torch.cat(ptr_parts).to(torch.int32)
-    col = torch.cat([m[1][: int(m[0][m[3]].item()) if m[3] > 0 else 0] for m in mats]) if nnz_base else torch.zeros(0, dtype=torch.int32, device=dev)
-    vals = torch.cat([m[2][: int(m[0][m[3]].item()) if m[3] > 0 else 0] for m in mats]) if (with_vals and nnz_base) else (
-        torch.zeros(0, dtype=torch.float16, device=dev) if with_vals else None)
-    K = max(m[4] for m in mats)
-    vec_ptr, vec_col, vec_val, replayed = svc(row_ptr, col.contiguous(), None if vals is None else vals.contiguous(), row_base, K, V)
-    out = []
-    cuts = vec_ptr[torch.tensor([b[0] for b in bases] + [row_base // V], device=dev)].tolist()
-    for k, (vr0, _) in enumerate(bases):
-        lo, hi = cuts[k], cuts[k + 1]
-        p = (vec_ptr[vr0: vr0 + m_vecs[k] + 1] - lo).contiguous()
-        out.append((p, vec_col[lo:hi], None if vec_val is None else vec_val[lo * V: hi * V]))
-    return out, replayed
+        _require(ci, torch.int32, "col_idx")
+        if with_vals:
+            _require(va, torch.float16, "values")
+    Ms = (C.c_int * n)(*[m[3] for m in mats])
+    Ks = (C.c_int * n)(*[m[4] for m in mats])
+    Zs = (C.c_int * n)(*nnz)
+    p_ptr = (C.c_void_p * n)(*[m[0].data_ptr() for m in mats])
+    p_col = (C.c_void_p * n)(*[m[1].data_ptr() for m in mats])
+    p_val = (C.c_void_p * n)(*[m[2].data_ptr() for m in mats]) if with_vals else None
+    nvec = (C.c_int64 * n)()
+    job = C.c_void_p()
+    lib = capi.lib()
+    with torch.cuda.device(dev):
+        st = _stream_ptr()
+        capi.check(lib.svc_batch_begin(n, V, Ms, Ks, Zs, p_ptr, p_col, p_val, st, C.byref(job), nvec))
+        try:
+            replayed = C.c_int64(0)
+            capi.check(lib.svc_batch_replayed_rows(job, C.byref(replayed)))
+            m_vecs = [(m[3] + V - 1) // V for m in mats]
+            total_vec = sum(nvec)
+            vec_ptr = torch.empty(sum(m_vecs) + n, dtype=torch.int32, device=dev)
+            vec_col = torch.empty(total_vec, dtype=torch.int32, device=dev)
+            vec_val = torch.empty(total_vec * V, dtype=torch.float16, device=dev) if with_vals else None
+            capi.check(lib.svc_batch_finish(job, vec_ptr.data_ptr(), vec_col.data_ptr(), _ptr(vec_val), st))
+        finally:
+            lib.svc_batch_free(job)
+    out, po, vo = [], 0, 0
+    for k in range(n):
+        nv = nvec[k]
+        out.append((vec_ptr[po: po + m_vecs[k] + 1], vec_col[vo: vo + nv], None if vec_val is None else vec_val[vo * V: (vo + nv) * V]))
+        po += m_vecs[k] + 1
+        vo += nv
+    return out, replayed.value
 
 
 def sorted_row_swizzle(row_offsets: torch.Tensor) -> torch.Tensor:
@@ -209,9 +217,13 @@ def sspmm_planned(plan: Plan, values: torch.Tensor, rhs: torch.Tensor, out_dtype
 
 class Group:
     """Several products bound to their operands and run as ONE persistent launch (``sspmm_group_create`` /
-    ``sspmm_group_run``).  ``products`` is a list of (plan, values, rhs, out); all outputs share one dtype."""
+    ``sspmm_group_run``).  ``products`` is a list of (plan, values, rhs, out); all outputs share one dtype.
+    ``mode``: COMPRESSED builds the A tiles inside the kernel (one launch, no scratch for A), EXPANDED writes dense
+    copies of A first (two launches, faster per K step), AUTO picks by the work per SM."""
 
-    def __init__(self, products):
+    AUTO, COMPRESSED, EXPANDED = 0, 1, 2
+
+    def __init__(self, products, mode: int = 0):
         import ctypes as C
         if not products:
             raise ValueError("a group needs at least one product")
@@ -228,10 +240,11 @@ class Group:
         self.device = products[0][2].device
         self._h = C.c_void_p()
         with torch.cuda.device(self.device):
-            capi.check(capi.lib().sspmm_group_create(arr, len(products), 1 if out_dtype == torch.float16 else 0, C.byref(self._h)))
-        bn, items, ctas, nbytes = C.c_int(), C.c_int(), C.c_int(), C.c_int64()
-        capi.check(capi.lib().sspmm_group_info(self._h, C.byref(bn), C.byref(items), C.byref(ctas), C.byref(nbytes)))
+            capi.check(capi.lib().sspmm_group_create(arr, len(products), 1 if out_dtype == torch.float16 else 0, mode, C.byref(self._h)))
+        bn, items, ctas, launches, nbytes = C.c_int(), C.c_int(), C.c_int(), C.c_int(), C.c_int64()
+        capi.check(capi.lib().sspmm_group_info(self._h, C.byref(bn), C.byref(items), C.byref(ctas), C.byref(launches), C.byref(nbytes)))
         self.tile_columns, self.work_items, self.ctas, self.scratch_bytes = bn.value, items.value, ctas.value, nbytes.value
+        self.launches = launches.value
 
     def run(self) -> None:
         if torch.cuda.current_device() == self.device.index:

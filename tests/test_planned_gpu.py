@@ -50,9 +50,10 @@ def test_ffn_v16_planned_and_grouped(lib, shape_id, sparsity_id):
     assert_close(got, ref)
     if plan.one_launch:
         d_val, d_rhs = dev(vals, rhs)
-        for dt in (torch.float16, torch.float32):
+        for dt, mode in ((torch.float16, ops.Group.COMPRESSED), (torch.float32, ops.Group.COMPRESSED), (torch.float16, ops.Group.EXPANDED)):
             out = torch.full((a.M, rhs.shape[1]), float("nan"), dtype=dt, device=DEV)
-            g = ops.Group([(plan, d_val, d_rhs, out)])
+            g = ops.Group([(plan, d_val, d_rhs, out)], mode=mode)
+            assert g.launches == (2 if mode == ops.Group.EXPANDED else 1)
             for _ in range(3):                         # the queue and the arrival counters reset themselves
                 out.fill_(float("nan"))
                 g.run()
@@ -94,9 +95,11 @@ def test_irregular_structure_falls_back(lib):
         ops.Group([(plan, d_val, d_rhs, torch.empty((16, 64), dtype=torch.float16, device=DEV))])
 
 
-def test_group_of_mixed_products(lib):
+@pytest.mark.parametrize("mode", [ops.Group.COMPRESSED, ops.Group.EXPANDED])
+def test_group_of_mixed_products(lib, mode):
     """Products of different shapes, V = 8 and 16, K from 64 to 2304, column counts with partial tiles, in one
-    launch; every product against the oracle; replays give bit-identical results."""
+    group (A tiles built in the kernel, or fetched from dense copies written at every run); every product against
+    the oracle; replays give bit-identical results."""
     rng = np.random.default_rng(77)
     shapes = [(256, 2304, 16, 0.9, 1000), (64, 576, 8, 0.8, 1000), (512, 128, 16, 0.8, 1000), (256, 64, 8, 0.9, 1000),
               (1024, 256, 8, 0.9, 328), (128, 1152, 16, 0.8, 328)]
@@ -111,7 +114,7 @@ def test_group_of_mixed_products(lib):
         out = torch.full((M, N), float("nan"), dtype=torch.float16, device=DEV)
         prods.append((plan, d_val, d_rhs, out))
         refs.append(spmm_oracle.sspmm_host(V, ptr, col, vals, rhs, threads=8))
-    g = ops.Group(prods)
+    g = ops.Group(prods, mode=mode)
     g.run()
     torch.cuda.synchronize()
     assert ops.device_status() == 0
@@ -142,12 +145,16 @@ def test_conv_layer_planned_wide(lib, N):
     assert plan.one_launch
     got = ops.sspmm_planned(plan, d_val, d_rhs)
     out = torch.full_like(got, float("nan"))
-    g = ops.Group([(plan, d_val, d_rhs, out)])
+    out2 = torch.full_like(got, float("nan"))
+    g = ops.Group([(plan, d_val, d_rhs, out)], mode=ops.Group.COMPRESSED)
+    g2 = ops.Group([(plan, d_val, d_rhs, out2)], mode=ops.Group.EXPANDED)
     g.run()
+    g2.run()
     torch.cuda.synchronize()
     assert ops.device_status() == 0
     a_np, b_np = got.float().cpu().numpy(), out.float().cpu().numpy()
     assert_close(b_np, a_np)
+    assert_close(out2.float().cpu().numpy(), a_np)
     for rows in ((0, 2), (15, 17), (a.M // V - 2, a.M // V)):
         ref = spmm_oracle.sspmm_host(V, ptr, col, vals, rhs, rows=rows, threads=8)
         assert_close(a_np[rows[0] * V: rows[1] * V], ref)
