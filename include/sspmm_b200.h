@@ -100,6 +100,21 @@ int sspmm_f16_f16_noalloc(int m_vec, int vec_length, int N, int K, const int* ro
  * sspmm_f16_f16_noalloc.
  */
 
+/*
+ * The same product as sspmm_f16_f16 for a caller that owns every buffer, as the reference's driver
+ * does (SSpMM/sspmm_test.cpp:108-127, 256-262): the vector count nvec = row_offsets[m_vec] is passed
+ * in (the compression returns it) and the scratch is the caller's, so the call reads nothing back,
+ * allocates nothing, remembers nothing and never synchronises.  sspmm_workspace_bytes reports what
+ * the kernel chosen for these sizes would like (0 for most sparse operands).  With less, long
+ * vector rows are not split (slower, same result); the dense-ish (block) kernel needs at least
+ * K * m_vec*V * 2 bytes and rejects less.  The workspace must stay untouched until the call's work
+ * on `stream` has finished; 256-byte alignment.
+ */
+int sspmm_workspace_bytes(int m_vec, int vec_length, int N, int K, int64_t nvec, int out_is_f16, int64_t* bytes);
+int sspmm_f16_f16_ws(int m_vec, int vec_length, int N, int K, const int* row_indices, const int* row_offsets,
+                     const int* column_indices, const void* values_f16, const void* rhs_f16, void* out_f16, int64_t nvec,
+                     void* workspace, int64_t workspace_bytes, void* stream);
+
 /* --------------------------------------------- plans and groups (one launch) --- */
 
 /*

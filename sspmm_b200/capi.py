@@ -19,6 +19,8 @@ SIGNATURES = {
     "sspmm_f16_f16": (C.c_int, [C.c_int] * 4 + [_vp] * 7),
     "sspmm_f16_f16_batched": (C.c_int, [C.c_int] * 5 + [_vp, _vp, _vp, _vp, C.c_int64, _vp, C.c_int64, _vp, C.c_int64, _vp]),
     "sspmm_f16_f16_noalloc": (C.c_int, [C.c_int] * 4 + [_vp] * 7),
+    "sspmm_workspace_bytes": (C.c_int, [C.c_int] * 4 + [C.c_int64, C.c_int, C.POINTER(C.c_int64)]),
+    "sspmm_f16_f16_ws": (C.c_int, [C.c_int] * 4 + [_vp] * 6 + [C.c_int64, _vp, C.c_int64, _vp]),
     "sspmm_plan_create": (C.c_int, [C.c_int] * 3 + [_vp, _vp, _vp, C.POINTER(_vp)]),
     "sspmm_plan_destroy": (C.c_int, [_vp]),
     "sspmm_plan_info": (C.c_int, [_vp, C.POINTER(C.c_int64), c_int_p, c_int_p, C.POINTER(C.c_int64)]),

@@ -132,9 +132,20 @@ __global__ void wait_expiry_selftest_kernel(int* gave_up) {
     }
 }
 
+// Caller-provided knowledge and room: with nvec >= 0 nothing is read back from the device, with a workspace nothing
+// is allocated.  query != null: only report the workspace size the chosen kernel wants, launch nothing.
+struct SpmmExtra {
+    long long nvec = -1;
+    void* workspace = nullptr;
+    size_t workspace_bytes = 0;
+    bool caller_workspace = false;
+    size_t* query = nullptr;
+};
+
 static int spmm_entry(int m_vec, int V, int N, int K, int batch, const int* row_indices, const int* row_offsets,
                       const int* column_indices, const void* values, int64_t values_stride, const void* rhs,
-                      int64_t rhs_stride, void* out, int64_t out_stride, bool out_f16, void* stream) {
+                      int64_t rhs_stride, void* out, int64_t out_stride, bool out_f16, void* stream,
+                      const SpmmExtra& ex = SpmmExtra()) {
     g_err[0] = 0;
     if (V != 8 && V != 16) {
         set_error("vec_length must be 8 or 16 (got %d)", V);
@@ -144,8 +155,9 @@ static int spmm_entry(int m_vec, int V, int N, int K, int batch, const int* row_
         set_error("negative dimension (m_vec=%d N=%d K=%d batch=%d)", m_vec, N, K, batch);
         return (int)cudaErrorInvalidValue;
     }
+    if (ex.query) *ex.query = 0;
     if (m_vec == 0 || N == 0 || batch == 0) return 0;
-    if (!row_offsets || !out || (K > 0 && (!column_indices || !values || !rhs))) {
+    if (!ex.query && (!row_offsets || !out || (K > 0 && (!column_indices || !values || !rhs)))) {
         set_error("null operand pointer");
         return (int)cudaErrorInvalidValue;
     }
@@ -167,6 +179,7 @@ static int spmm_entry(int m_vec, int V, int N, int K, int batch, const int* row_
     }
     cudaError_t e;
     if (K == 0 || choice == 2 || !tc_ok) {
+        if (ex.query) return 0;
         e = launch_sspmm_simt(a);
         return e == cudaSuccess ? 0 : fail(e, "SpMM launch");
     }
@@ -179,32 +192,49 @@ static int spmm_entry(int m_vec, int V, int N, int K, int batch, const int* row_
         return (int)cudaErrorInvalidValue;
     }
     if (choice == 1) {                                     // TMA row-gather producers
+        if (ex.query) return 0;
         e = launch_sspmm_gather(a);
         return e == cudaSuccess ? 0 : fail(e, "SpMM launch");
     }
     bool use_block = choice == 3;
-    long long nvec = -1;
-    if (choice == 0 || choice == 4) nvec = lookup_nvec(row_offsets, m_vec, st);
+    long long nvec = ex.nvec;
+    if (nvec < 0 && !ex.query && (choice == 0 || choice == 4)) nvec = lookup_nvec(row_offsets, m_vec, st);
     if (choice == 0 && block_ok) use_block = nvec >= 0 && block_kernel_is_faster(nvec, a);
     if (!use_block) {                                      // gather kernel with load-instruction producers
         int chunk = 0, cap = 0;
         size_t bytes = 0;
         sspmm_gather_lsu_plan(a, nvec, &chunk, &cap, &bytes);
+        if (ex.query) { *ex.query = bytes; return 0; }
         void* scratch = nullptr;
-        if (bytes) {
+        if (ex.caller_workspace) {
+            if (bytes > ex.workspace_bytes) { chunk = 0; cap = 0; bytes = 0; }     // too small: long rows are not split (slower, same result)
+            else scratch = ex.workspace;
+        } else if (bytes) {
             keep_pool_memory();
             e = cudaMallocAsync(&scratch, bytes, st);
             if (e != cudaSuccess) return fail(e, "scratch allocation for split rows");
         }
-        e = launch_sspmm_gather_lsu(a, chunk, cap, scratch);
-        if (scratch) cudaFreeAsync(scratch, st);
+        e = launch_sspmm_gather_lsu(a, chunk, cap, bytes ? scratch : nullptr);
+        if (scratch && !ex.caller_workspace) cudaFreeAsync(scratch, st);
+        return e == cudaSuccess ? 0 : fail(e, "SpMM launch");
+    }
+    const size_t want = sspmm_block_scratch_bytes(a);
+    if (ex.query) { *ex.query = want; return 0; }
+    if (ex.caller_workspace) {
+        const size_t need = (size_t)K * m_vec * V * sizeof(__half);
+        if (ex.workspace_bytes < need || !ex.workspace) {
+            set_error("workspace of %zu bytes is too small: the block kernel needs at least %zu (sspmm_workspace_bytes reports %zu)",
+                      ex.workspace_bytes, need, want);
+            return (int)cudaErrorInvalidValue;
+        }
+        e = launch_sspmm_block(a, ex.workspace, ex.workspace_bytes);
         return e == cudaSuccess ? 0 : fail(e, "SpMM launch");
     }
     void* scratch = nullptr;
     keep_pool_memory();
-    e = cudaMallocAsync(&scratch, sspmm_block_scratch_bytes(a), st);
+    e = cudaMallocAsync(&scratch, want, st);
     if (e != cudaSuccess) return fail(e, "scratch allocation for the block kernel");
-    e = launch_sspmm_block(a, scratch, sspmm_block_scratch_bytes(a));
+    e = launch_sspmm_block(a, scratch, want);
     cudaFreeAsync(scratch, st);
     return e == cudaSuccess ? 0 : fail(e, "SpMM launch");
 }
@@ -256,6 +286,29 @@ int sspmm_f16_f16_batched(int m_vec, int vec_length, int N, int K, int batch, co
                           int64_t out_stride, void* stream) {
     return spmm_entry(m_vec, vec_length, N, K, batch, row_indices, row_offsets, column_indices, values_f16,
                       values_stride, rhs_f16, rhs_stride, out_f16, out_stride, true, stream);
+}
+
+int sspmm_workspace_bytes(int m_vec, int vec_length, int N, int K, int64_t nvec, int out_is_f16, int64_t* bytes) {
+    if (!bytes || nvec < 0) { g_err[0] = 0; set_error("bytes must be non-null and nvec >= 0"); return (int)cudaErrorInvalidValue; }
+    SpmmExtra ex;
+    size_t q = 0;
+    ex.nvec = nvec; ex.query = &q;
+    // aligned dummy operands: only sizes and alignment enter the choice of kernel
+    void* dummy = reinterpret_cast<void*>(uintptr_t(256));
+    const int rc = spmm_entry(m_vec, vec_length, N, K, 1, nullptr, nullptr, nullptr, dummy, 0, dummy, 0, dummy, 0, out_is_f16 != 0,
+                              nullptr, ex);
+    *bytes = (int64_t)q;
+    return rc;
+}
+
+int sspmm_f16_f16_ws(int m_vec, int vec_length, int N, int K, const int* row_indices, const int* row_offsets,
+                     const int* column_indices, const void* values_f16, const void* rhs_f16, void* out_f16, int64_t nvec,
+                     void* workspace, int64_t workspace_bytes, void* stream) {
+    if (nvec < 0 || workspace_bytes < 0) { g_err[0] = 0; set_error("nvec and workspace_bytes must be >= 0"); return (int)cudaErrorInvalidValue; }
+    SpmmExtra ex;
+    ex.nvec = nvec; ex.workspace = workspace; ex.workspace_bytes = (size_t)workspace_bytes; ex.caller_workspace = true;
+    return spmm_entry(m_vec, vec_length, N, K, 1, row_indices, row_offsets, column_indices, values_f16, 0, rhs_f16, 0, out_f16, 0,
+                      true, stream, ex);
 }
 
 int sspmm_set_kernel(int which) {

@@ -29,6 +29,7 @@ class SparseLinear:
         self.row_offsets, self.col, self.values, _ = ops.svc(d(weight.row_ptr), d(weight.col_idx), d(weight.values),
                                                              weight.M, weight.K, vec_length)
         self.row_indices = ops.sorted_row_swizzle(self.row_offsets)
+        self.plan = ops.Plan(self.row_offsets, self.col, vec_length, weight.K)
         self.bias = bias
         self.dense = torch.from_numpy(weight.dense()).to(device)          # only for the dense comparison
 
@@ -68,6 +69,41 @@ class SparseEncoderLayer:
             return t.view(h, hd, batch, seq).permute(2, 0, 3, 1)
         o = F.scaled_dot_product_attention(split(q), split(k), split(v))
         return o.permute(1, 3, 0, 2).reshape(self.hidden, batch * seq)
+
+    def _groups_for(self, tokens: int):
+        """Activation buffers of fixed shape and, bound to them, one group per dependency level of the layer:
+        {Q, K, V} share their input and run as one launch, then O, FFN1, FFN2."""
+        if getattr(self, "_tokens", None) == tokens:
+            return
+        z = lambda rows: torch.empty((rows, tokens), dtype=torch.float16, device=self.dev)
+        b = self.buf = {"ln1": z(self.hidden), "q": z(self.hidden), "k": z(self.hidden), "v": z(self.hidden),
+                        "att": z(self.hidden), "o": z(self.hidden), "ln2": z(self.hidden), "h": z(self.ffn), "y": z(self.hidden)}
+        L = self.linears
+        item = lambda l, src, dst: (l.plan, l.values, b[src], b[dst])
+        self.groups = None
+        if all(l.plan.one_launch and l.out_features % l.V == 0 for l in L):
+            self.groups = [ops.Group([item(L[0], "ln1", "q"), item(L[1], "ln1", "k"), item(L[2], "ln1", "v")]),
+                           ops.Group([item(L[3], "att", "o")]), ops.Group([item(L[4], "ln2", "h")]),
+                           ops.Group([item(L[5], "h", "y")])]
+        self._tokens = tokens
+
+    def forward_grouped(self, x: torch.Tensor, batch: int, seq: int) -> torch.Tensor:
+        """Same layer with the linears run as groups (sspmm_group_run) on preallocated activation buffers."""
+        self._groups_for(batch * seq)
+        if self.groups is None:
+            return self.forward(x, batch, seq)
+        b, L, g = self.buf, self.linears, self.groups
+        b["ln1"].copy_(self._layer_norm_fm(x, self.ln1))
+        g[0].run()
+        q, k, v = (b[n] + L[i].bias[:, None] for i, n in enumerate(("q", "k", "v")))
+        b["att"].copy_(self._attention(q, k, v, batch, seq))
+        g[1].run()
+        out = b["o"] + L[3].bias[:, None] + x
+        b["ln2"].copy_(self._layer_norm_fm(out, self.ln2))
+        g[2].run()
+        b["h"] += L[4].bias[:, None]
+        g[3].run()
+        return b["y"] + L[5].bias[:, None] + out
 
     def forward(self, x: torch.Tensor, batch: int, seq: int, dense: bool = False) -> torch.Tensor:
         """x: [hidden, batch*seq] fp16, feature-major (token t of sequence b is column b*seq + t)."""

@@ -265,3 +265,31 @@ class Group:
             self.close()
         except Exception:
             pass
+
+
+def workspace_bytes(m_vec: int, vec_length: int, N: int, K: int, nvec: int, out_is_f16: bool = True) -> int:
+    """Scratch ``sspmm_ws`` would like for these sizes (``sspmm_workspace_bytes``)."""
+    import ctypes as C
+    b = C.c_int64(0)
+    capi.check(capi.lib().sspmm_workspace_bytes(m_vec, vec_length, N, K, nvec, 1 if out_is_f16 else 0, C.byref(b)))
+    return b.value
+
+
+def sspmm_ws(row_offsets: torch.Tensor, column_indices: torch.Tensor, values: torch.Tensor, rhs: torch.Tensor,
+             vec_length: int, nvec: int, workspace: Optional[torch.Tensor], out: Optional[torch.Tensor] = None,
+             row_indices: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """C = A_vs @ rhs through ``sspmm_f16_f16_ws``: the caller passes the vector count and owns the scratch, so the
+    library reads nothing back, allocates nothing and never synchronises."""
+    m_vec = row_offsets.numel() - 1
+    K, N = rhs.shape
+    if out is None:
+        out = torch.empty((m_vec * vec_length, N), dtype=torch.float16, device=rhs.device)
+    ws_ptr = workspace.data_ptr() if workspace is not None else None
+    ws_bytes = workspace.numel() * workspace.element_size() if workspace is not None else 0
+    with torch.cuda.device(rhs.device):
+        rc = capi.lib().sspmm_f16_f16_ws(m_vec, vec_length, N, K, _ptr(row_indices), row_offsets.data_ptr(),
+                                         column_indices.data_ptr(), values.data_ptr(), rhs.data_ptr(), out.data_ptr(),
+                                         nvec, ws_ptr, ws_bytes, _stream_ptr())
+    if rc != 0:
+        capi.check(rc)
+    return out

@@ -84,6 +84,49 @@ def power_law(n: int, rng: np.random.Generator, mean_nnz: float = 16.0) -> CSR:
     return CSR(n, n, row_ptr.astype(np.int32), cols, vals)
 
 
+def power_law_device(n: int, seed: int, device, mean_nnz: float = 16.0):
+    """The distribution of ``power_law`` (row lengths from Zipf(2) truncated at n and rescaled to the mean, uniform
+    column ids without replacement, ascending inside a row, values U(-1, 1) in fp16) drawn on the GPU with torch's
+    seeded generator: a sweep of thousands of matrices is generated in seconds.  Returns device tensors
+    (row_ptr int32 [n+1], col_idx int32 [nnz], values fp16 [nnz]).  Not the same matrices as ``power_law``."""
+    import torch
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    k = torch.arange(1, n + 1, device=device, dtype=torch.float64)
+    cdf = torch.cumsum(k ** -2.0, 0)
+    cdf /= cdf[-1].clone()
+    z = (torch.searchsorted(cdf, torch.rand(n, device=device, dtype=torch.float64, generator=g)) + 1).clamp_(max=n).double()
+    ln = torch.clamp(torch.round(mean_nnz * z / z.mean()), 1, n).long()
+    heavy = ln * 4 > n
+    want = torch.where(heavy, torch.zeros_like(ln), ln)
+    # light rows: oversample, keep each row's distinct draws, thin the surplus at random
+    over = torch.where(heavy, torch.zeros_like(ln), want + 8 + want // 4)
+    rows = torch.repeat_interleave(torch.arange(n, device=device), over)
+    keys = torch.unique(rows * n + torch.randint(0, n, (rows.numel(),), device=device, generator=g))
+    krow = keys // n
+    have = torch.bincount(krow, minlength=n)
+    redo = heavy | (have < want)                              # heavy rows, and (rare) rows short of distinct draws
+    prio = torch.rand(keys.numel(), device=device, generator=g)
+    order = torch.argsort(krow.double() + prio)                # inside a row: random order (prio < 1)
+    start = torch.cumsum(have, 0) - have
+    ko = krow[order]
+    rank = torch.arange(keys.numel(), device=device) - start[ko]
+    keep = order[(rank < want[ko]) & ~redo[ko]]
+    kept = keys[keep]
+    extra = []
+    for r in torch.nonzero(redo).flatten().tolist():
+        pick = torch.randperm(n, device=device, generator=g)[: int(ln[r])]
+        extra.append(r * n + pick)
+    if extra:
+        kept = torch.cat([kept] + extra)
+    kept, _ = torch.sort(kept)
+    row_ptr = torch.zeros(n + 1, device=device, dtype=torch.int64)
+    row_ptr[1:] = torch.cumsum(torch.bincount(kept // n, minlength=n), 0)
+    col = (kept % n).int()
+    vals = (torch.rand(col.numel(), device=device, generator=g) * 2 - 1).half()
+    return row_ptr.int(), col, vals
+
+
 # ---- named configurations ------------------------------------------------- #
 
 FFN_SHAPES = [(2048, 512), (512, 2048)]
@@ -136,3 +179,9 @@ def sweep_matrix(matrix_id: int) -> CSR:
     rng = np.random.default_rng(5000 + matrix_id)
     n = int(round(4096 * 16.0 ** rng.random()))
     return power_law(n, rng)
+
+
+def sweep_matrix_device(matrix_id: int, device):
+    """Matrix `matrix_id` of the 2000-matrix sweep, drawn on the GPU: n from the same seed rule as ``sweep_matrix``."""
+    n = sweep_size(matrix_id)
+    return (n,) + tuple(power_law_device(n, 5000 + matrix_id, device))

@@ -60,7 +60,7 @@ def test_config1(lib, V, out_dtype, kernel):
     assert_close(got, ref, fp32=out_dtype == torch.float32)
 
 
-@pytest.mark.parametrize("shape_id,sparsity_id", [(0, 0), (0, 3), (0, 5), (1, 1), (1, 3), (1, 5)])
+@pytest.mark.parametrize("shape_id,sparsity_id", [(sh, sp) for sh in range(2) for sp in range(6)])
 def test_ffn_v16(lib, shape_id, sparsity_id):
     a, rhs = synthetic.ffn(shape_id, sparsity_id)
     ptr, col, vals = compress(a, 16)
