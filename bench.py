@@ -932,6 +932,72 @@ def bench_ffn(torch, ops, dev, peaks):
             "cases": out}
 
 
+def run_case(name: str):
+    """Small fixed workloads for profiler captures (one kernel family, a few launches, a few GB at most):
+         group_conv_shard   the 32 conv products as one group at the 8-GPU shard width N = 3136, three runs
+         group_conv_full    the same at N = 25088 (the benchmark step), three runs
+         group_conv_layer   conv layer (512, 4608) s = 0.8 V = 16, N = 18944, as a group, expanded and compressed
+         planned_conv_layer the same layer through sspmm_planned (one launch, A tiles built in the kernel), N = 9472
+         sweep_stack        32 sweep matrices: stacked SVC (svc_batch), then the SpMM of each at N = 128
+         svc_powerlaw       SVC of one power-law matrix, n = 65536, V = 8, three times
+         gather_powerlaw    row-gather SpMM of that matrix at N = 1024, four times"""
+    import torch
+    from sspmm_b200 import build, capi, ops
+    build.build()
+    capi.lib()
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(0)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    up = lambda a: (torch.from_numpy(a.row_ptr).to(dev), torch.from_numpy(a.col_idx).to(dev), torch.from_numpy(a.values).to(dev))
+
+    def conv_product(l, s, V, N):
+        a = synthetic.conv_weight(l, s)
+        vp, vc, vv, _ = ops.svc(*up(a), a.M, a.K, V)
+        B = torch.randn((a.K, N), device=dev, dtype=torch.float16)
+        C = torch.empty(((vp.numel() - 1) * V, N), device=dev, dtype=torch.float16)
+        return ops.Plan(vp, vc, V, a.K), vv, B, C
+    if name in ("group_conv_shard", "group_conv_full"):
+        g = ops.Group([conv_product(l, s, V, 3136 if name == "group_conv_shard" else synthetic.CONV_N) for (l, s, V) in conv_problems()])
+        for _ in range(3):
+            flush.zero_()
+            g.run()
+    elif name == "group_conv_layer":
+        prod = conv_product(3, 0, 16, 18944)
+        for mode in (ops.Group.EXPANDED, ops.Group.COMPRESSED):
+            g = ops.Group([prod], mode=mode)
+            for _ in range(2):
+                flush.zero_()
+                g.run()
+    elif name == "planned_conv_layer":
+        plan, vv, B, C = conv_product(3, 0, 16, 9472)
+        for _ in range(3):
+            flush.zero_()
+            ops.sspmm_planned(plan, vv, B, out=C)
+    elif name == "sweep_stack":
+        mats = [synthetic.sweep_matrix_device(i, dev) for i in range(32)]
+        ws = torch.empty(64 << 20, dtype=torch.uint8, device=dev)
+        for _ in range(2):
+            parts, _ = ops.svc_batch([(p, c, v, n, n) for n, p, c, v in mats], 8)
+            for (n, p, c, v), (vp, vc, vv) in zip(mats, parts):
+                B = torch.randn((n, 128), device=dev, dtype=torch.float16)
+                ops.sspmm_ws(vp, vc, vv, B, 8, vc.numel(), ws)
+    elif name in ("svc_powerlaw", "gather_powerlaw"):
+        p, c, v = synthetic.power_law_device(65536, 65536, dev)
+        for _ in range(3):
+            vp, vc, vv, _ = ops.svc(p, c, v, 65536, 65536, 8)
+        if name == "gather_powerlaw":
+            B = torch.randn((65536, 1024), device=dev, dtype=torch.float16)
+            C = torch.empty((65536, 1024), device=dev, dtype=torch.float16)
+            ws = torch.empty(max(ops.workspace_bytes(8192, 8, 1024, 65536, vc.numel()), 256), dtype=torch.uint8, device=dev)
+            for _ in range(4):
+                ops.sspmm_ws(vp, vc, vv, B, 8, vc.numel(), ws, out=C)
+    else:
+        raise SystemExit(run_case.__doc__)
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    print(json.dumps({"case": name, "status": "done"}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -944,6 +1010,7 @@ def main():
     ap.add_argument("--sweep-matrices", type=int, default=2000, help="matrices of the power-law sweep (whole job)")
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of a CUDA graph of the step")
     ap.add_argument("--no-extras", action="store_true", help="skip the SVC and FFN side measurements")
+    ap.add_argument("--case", default="", help="run one small fixed workload for a profiler capture and exit (see run_case)")
     ap.add_argument("--only", default="", help="layer_id,sparsity_id,V: run a single product (profiling captures)")
     args = ap.parse_args()
     # a run that stalls ends with a traceback on stderr instead of holding the GPU until it is killed
@@ -954,7 +1021,9 @@ def main():
     os.dup2(2, 1)
     out = io.StringIO()
     with contextlib.redirect_stdout(out):
-        if args.impl == "reference":
+        if args.case:
+            run_case(args.case)
+        elif args.impl == "reference":
             run_reference(args)
         else:
             run_ours(args)

@@ -647,78 +647,77 @@ sspmm_fused_kernel(const __grid_constant__ Params gp) {
 
 // ---- expansion of the compressed operands of a group ---------------------------------------
 // At[k][i*V .. i*V+V) = value vector of vector row i at column k, or zeros; every element of At is written, so
-// nothing from an earlier run survives.  One CTA per (product, chunk of 1024 columns, row slot): the row's column
-// list becomes a column -> vector map in shared memory, then every column of the chunk is written.
+// nothing from an earlier run survives.  One thread per (vector row i, eight columns of a 64-column step): the
+// plan's metadata tells it which of its columns carry a vector and where, so a thread is two dependent reads
+// (metadata, value vectors) and its stores, with no shared memory and no barrier; consecutive threads have
+// consecutive i, so the stores of a warp to a row of At are contiguous.
 struct ExpandJob {
-    const int* row_offsets;
-    const int* col;
+    const uint4* meta;             // the plan's column masks, or null
+    const int* posmap;             // the plan's positions (when meta is null)
     const __half* values;
     __half* at;
-    int m_vec, K, V, chunks;       // chunks = ceil(K / 1024)
-    int slots;                     // CTAs that share the vector rows of one chunk
-    int unit_base;                 // first unit (CTA) of this job
+    int m_vec, K, V, k_steps;
+    int block_base;                // first thread block of this job
 };
-constexpr int kExpandChunk = 1024;
 
 template <int V>
-__device__ __forceinline__ void expand_rows(const ExpandJob& job, int chunk, int slot, int* col_to_vec) {
+__device__ __forceinline__ void expand_slots(const ExpandJob& job, int id) {
+    using A = ATile<V>;
+    const int i = id % job.m_vec;
+    const int g = (id / job.m_vec) & 7;
+    const int ks = id / (job.m_vec * 8);
+    if (ks >= job.k_steps) return;
+    const int tile = i / A::R, r = i % A::R;
+    const int64_t stage = (int64_t)tile * job.k_steps + ks;
+    int jj[8];
+    if (job.meta) {
+        const uint4 m = __ldg(job.meta + stage * A::R + r);
+        const unsigned long long mask = (unsigned long long)m.x | ((unsigned long long)m.y << 32);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            const int kk = g * 8 + q;
+            jj[q] = ((mask >> kk) & 1ull) ? (int)m.z + __popcll(mask & ((1ull << kk) - 1ull)) : -1;
+        }
+    } else {
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            const int kk = g * 8 + q;
+            jj[q] = __ldg(job.posmap + (stage * kGroupThreads + r * A::TPR + kk % A::TPR) * A::SLOTS + kk / A::TPR);
+        }
+    }
+    uint4 v[8][V / 8];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+        const uint4* src = reinterpret_cast<const uint4*>(job.values + (int64_t)(jj[q] >= 0 ? jj[q] : 0) * V);
+#pragma unroll
+        for (int h = 0; h < V / 8; ++h) v[q][h] = jj[q] >= 0 ? __ldg(src + h) : make_uint4(0u, 0u, 0u, 0u);
+    }
     const int64_t mp = (int64_t)job.m_vec * V;
-    const int k_begin = chunk * kExpandChunk;
-    const int k_end = min(job.K, k_begin + kExpandChunk);
-    for (int i = slot; i < job.m_vec; i += job.slots) {
-        for (int k = threadIdx.x; k < kExpandChunk; k += blockDim.x) col_to_vec[k] = -1;
-        __syncthreads();
-        const int j0 = job.row_offsets[i], j1 = job.row_offsets[i + 1];
-        for (int j = j0 + threadIdx.x; j < j1; j += 4 * blockDim.x) {      // four independent loads in flight
-            int c[4];
 #pragma unroll
-            for (int q = 0; q < 4; ++q) c[q] = (j + q * (int)blockDim.x < j1) ? __ldg(job.col + j + q * blockDim.x) : -1;
+    for (int q = 0; q < 8; ++q) {
+        const int k = ks * kBK + g * 8 + q;
+        if (k < job.K) {
+            uint4* dst = reinterpret_cast<uint4*>(job.at + (int64_t)k * mp + (int64_t)i * V);
 #pragma unroll
-            for (int q = 0; q < 4; ++q)
-                if (c[q] >= k_begin && c[q] < k_end) col_to_vec[c[q] - k_begin] = j + q * blockDim.x;
+            for (int h = 0; h < V / 8; ++h) dst[h] = v[q][h];
         }
-        __syncthreads();
-        for (int k = k_begin + threadIdx.x; k < k_end; k += 4 * blockDim.x) {
-            int js[4];
-            uint4 v[4][V / 8];
-#pragma unroll
-            for (int q = 0; q < 4; ++q) js[q] = (k + q * (int)blockDim.x < k_end) ? col_to_vec[k + q * blockDim.x - k_begin] : -1;
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                const uint4* src = reinterpret_cast<const uint4*>(job.values + (int64_t)(js[q] >= 0 ? js[q] : 0) * V);
-#pragma unroll
-                for (int h = 0; h < V / 8; ++h) v[q][h] = js[q] >= 0 ? __ldg(src + h) : make_uint4(0, 0, 0, 0);
-            }
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                const int kq = k + q * (int)blockDim.x;
-                if (kq < k_end) {
-                    uint4* dst = reinterpret_cast<uint4*>(job.at + (int64_t)kq * mp + (int64_t)i * V);
-#pragma unroll
-                    for (int h = 0; h < V / 8; ++h) dst[h] = v[q][h];
-                }
-            }
-        }
-        __syncthreads();
     }
 }
 
 __global__ void __launch_bounds__(256)
 expand_group_kernel(const ExpandJob* __restrict__ jobs, int n_jobs) {
-    __shared__ int col_to_vec[kExpandChunk];
     __shared__ ExpandJob job;
     if (threadIdx.x == 0) {
         int lo = 0, hi = n_jobs - 1;
         while (lo < hi) {
             const int mid = (lo + hi + 1) >> 1;
-            if (jobs[mid].unit_base <= (int)blockIdx.x) lo = mid; else hi = mid - 1;
+            if (jobs[mid].block_base <= (int)blockIdx.x) lo = mid; else hi = mid - 1;
         }
         job = jobs[lo];
     }
     __syncthreads();
-    const int local = (int)blockIdx.x - job.unit_base;
-    const int chunk = local % job.chunks, slot = local / job.chunks;
-    if (job.V == 16) expand_rows<16>(job, chunk, slot, col_to_vec); else expand_rows<8>(job, chunk, slot, col_to_vec);
+    const int id = ((int)blockIdx.x - job.block_base) * 256 + (int)threadIdx.x;
+    if (job.V == 16) expand_slots<16>(job, id); else expand_slots<8>(job, id);
 }
 
 // ---- plan construction ------------------------------------------------------------------
@@ -1175,13 +1174,11 @@ int sspmm_group_create(const sspmm_group_item* items, int count, int out_is_f16,
             at_off[i] = at_bytes;
             at_bytes += up((size_t)pl->K * pl->m_vec * pl->V * sizeof(__half));
             fused::ExpandJob& j = jobs[i];
-            j.row_offsets = pl->row_offsets; j.col = pl->column_indices;
+            j.meta = pl->meta; j.posmap = pl->posmap;
             j.values = static_cast<const __half*>(items[i].values_f16); j.at = nullptr;
-            j.m_vec = pl->m_vec; j.K = pl->K; j.V = pl->V;
-            j.chunks = (pl->K + fused::kExpandChunk - 1) / fused::kExpandChunk;
-            j.slots = pl->m_vec < 2048 ? pl->m_vec : 2048;       // one vector row per CTA: the kernel is a chain of dependent reads
-            j.unit_base = g->expand_units;
-            g->expand_units += j.chunks * j.slots;
+            j.m_vec = pl->m_vec; j.K = pl->K; j.V = pl->V; j.k_steps = pl->k_steps;
+            j.block_base = g->expand_units;
+            g->expand_units += (int)(((int64_t)pl->m_vec * 8 * pl->k_steps + 255) / 256);
         }
     }
     const size_t off_items = up(probs.size() * sizeof(fused::Problem));
