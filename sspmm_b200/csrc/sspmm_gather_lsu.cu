@@ -358,23 +358,26 @@ __global__ void __launch_bounds__(128)
 sum_chunks_kernel(int N, int n_tiles, int chunk, int cap, const int* __restrict__ row_offsets,
                   const int* __restrict__ n_entries, const int2* __restrict__ entries, const float* __restrict__ partial,
                   OutT* __restrict__ out) {
-    const int e = blockIdx.y;
-    if (*n_entries > cap || e >= *n_entries) return;
-    const int2 en = entries[e];
-    if (en.y != 0) return;
-    const int len = row_offsets[en.x + 1] - row_offsets[en.x];
-    const int n_chunks = (len + chunk - 1) / chunk;
+    const int total = *n_entries;
+    if (total > cap) return;
     const int t = blockIdx.x;
     const int n = t * kTileN + threadIdx.x;
     if (n >= N) return;
+    // the entry list is usually far shorter than its capacity: a bounded grid walks it
+    for (int e = blockIdx.y; e < total; e += gridDim.y) {
+        const int2 en = entries[e];
+        if (en.y != 0) continue;
+        const int len = row_offsets[en.x + 1] - row_offsets[en.x];
+        const int n_chunks = (len + chunk - 1) / chunk;
 #pragma unroll
-    for (int v = 0; v < V; ++v) {
-        float acc = 0.f;
-        for (int c = 0; c < n_chunks; ++c)
-            acc += partial[((int64_t)(e + c) * n_tiles + t) * V * kTileN + v * kTileN + threadIdx.x];
-        const int64_t o = ((int64_t)en.x * V + v) * N + n;
-        if constexpr (sizeof(OutT) == 2) out[o] = __float2half_rn(acc);
-        else out[o] = acc;
+        for (int v = 0; v < V; ++v) {
+            float acc = 0.f;
+            for (int c = 0; c < n_chunks; ++c)
+                acc += partial[((int64_t)(e + c) * n_tiles + t) * V * kTileN + v * kTileN + threadIdx.x];
+            const int64_t o = ((int64_t)en.x * V + v) * N + n;
+            if constexpr (sizeof(OutT) == 2) out[o] = __float2half_rn(acc);
+            else out[o] = acc;
+        }
     }
 }
 
@@ -400,7 +403,7 @@ cudaError_t launch_typed(const SpmmArgs& a, Problem p, int cap, void* scratch, i
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     if (p.chunk > 0) {
-        dim3 g(p.n_tiles, cap);
+        dim3 g(p.n_tiles, cap < 592 ? cap : 592);
         sum_chunks_kernel<V, OutT><<<g, 128, 0, a.stream>>>(a.N, p.n_tiles, p.chunk, cap, a.row_offsets, p.n_entries, p.entries,
                                                             p.partial, static_cast<OutT*>(a.out));
         e = cudaGetLastError();
