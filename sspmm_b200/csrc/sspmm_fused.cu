@@ -63,7 +63,8 @@ constexpr int kRing = 32;
 // memory (group); 64-byte aligned because of the tensor maps.
 struct alignas(64) Problem {
     CUtensorMap tmap_a;        // expanded mode only: At {M', K, 1} fp16 (dense transposed copy of A), box 64 x 64, 128-byte swizzle
-    CUtensorMap tmap_b;        // B  {N, K, 1}   fp16, box 64 x 64, 128-byte swizzle
+    CUtensorMap tmap_b;        // B  {N, K, 1}   fp16, box 64 x 64, 128-byte swizzle (or the chunked view, see `wide`)
+    CUtensorMap tmap_b1;       // chunked view of B with a one-chunk box: the last, partly filled column tile fetches only its own chunks
     CUtensorMap tmap_c;        // C  {N, M', 1}  fp16/fp32, box (64 bytes) x 128 rows, 64-byte swizzle
     const uint4* meta;         // plan, ascending rows: [m_tile][k_step][row in tile] {mask lo, mask hi, start, 0}
     const int* posmap;         // plan, other structures: [m_tile][k_step][loader thread][slot] index of the vector or -1
@@ -71,6 +72,7 @@ struct alignas(64) Problem {
     void* out;
     int Mp, N, K, V;
     int k_steps, m_tiles, n_tiles;
+    int expand_blocks;         // expanded mode: blocks of the expansion of this product's A (see ExpandJob)
     int wide;                  // bit 0: tmap_b, bit 1: tmap_a are chunked views {64, rows, width / 64}: one TMA request brings all chunks of a tile
 };
 static_assert(sizeof(Problem) % 64 == 0, "Problem must keep the tensor maps 64-byte aligned in arrays");
@@ -82,14 +84,21 @@ struct Item {
     int prob, m_tile, n_tile, ks0, ks1, pslot, pp /* part | parts << 8 */, cslot;
 };
 
+struct ExpandJob;
+
 struct Params {
     const Problem* probs;      // device array, or null: inline_prob
     const Item* items;         // device array, or null: every tile of inline_prob once, whole K range
     int n_items;
     int dynamic;               // 1: items are taken from queue[0] (grid-wide atomic), else CTA b takes b, b + grid, ...
-    int* queue;                // [0] next item, [1] CTAs that finished taking items (the last one resets both)
+    int* queue;                // [0] next item, [1] CTAs that have left (the last one resets both, and expand_state)
     float* partials;
     int* counters;
+    // expanded mode: the loader warps write the dense copies of A block by block (expand_state[0] = next block),
+    // expand_state[2 + p] counts the finished blocks of product p, expand_state[1] the CTAs that have left
+    const ExpandJob* jobs;
+    int n_jobs, expand_blocks;
+    int* expand_state;
     Problem inline_prob;
 };
 
@@ -116,6 +125,14 @@ struct Layout {
     static constexpr uint32_t kTmemCols = 2 * BN;                // 128, 256 or 512
     static_assert(kDynamic <= 227 * 1024, "shared memory of one CTA");
 };
+
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+// orders earlier generic-proxy accesses (made visible to this thread) before later async-proxy (TMA) accesses, global memory included
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
 
 __device__ __forceinline__ void fence_tensormap_acquire(const void* tmap) {
     // a tensor map that was written to global memory by a copy is read through its own proxy
@@ -173,6 +190,67 @@ struct StageDesc {
     int V;               // 8 or 16, + 32 when the metadata words are positions; 0 = no stage (end of the sequence)
 };
 
+// ---- expansion of the compressed operands of a group ---------------------------------------
+// At[k][i*V .. i*V+V) = value vector of vector row i at column k, or zeros; every element of At is written, so
+// nothing from an earlier run survives.  One thread per (vector row i, eight columns of a 64-column step): the
+// plan's metadata tells it which of its columns carry a vector and where, so a thread is two dependent reads
+// (metadata, value vectors) and its stores; consecutive threads have consecutive i, so the stores of a warp to a
+// row of At are contiguous.  The work is cut into blocks of 256 threads, which the loader warps of the tensor-core
+// kernel (idle when A tiles come by TMA) take from a counter while the other warps already multiply.
+struct ExpandJob {
+    const uint4* meta;             // the plan's column masks, or null
+    const int* posmap;             // the plan's positions (when meta is null)
+    const __half* values;
+    __half* at;
+    int m_vec, K, V, k_steps;
+    int block_base;                // first block of this job (jobs are sorted by it)
+    int prob;                      // the product whose copy this job writes
+};
+
+template <int V>
+__device__ __forceinline__ void expand_slots(const ExpandJob& job, int id) {
+    using A = ATile<V>;
+    const int i = id % job.m_vec;
+    const int g = (id / job.m_vec) & 7;
+    const int ks = id / (job.m_vec * 8);
+    if (ks >= job.k_steps) return;
+    const int tile = i / A::R, r = i % A::R;
+    const int64_t stage = (int64_t)tile * job.k_steps + ks;
+    int jj[8];
+    if (job.meta) {
+        const uint4 m = __ldg(job.meta + stage * A::R + r);
+        const unsigned long long mask = (unsigned long long)m.x | ((unsigned long long)m.y << 32);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            const int kk = g * 8 + q;
+            jj[q] = ((mask >> kk) & 1ull) ? (int)m.z + __popcll(mask & ((1ull << kk) - 1ull)) : -1;
+        }
+    } else {
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            const int kk = g * 8 + q;
+            jj[q] = __ldg(job.posmap + (stage * kGroupThreads + r * A::TPR + kk % A::TPR) * A::SLOTS + kk / A::TPR);
+        }
+    }
+    uint4 v[8][V / 8];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+        const uint4* src = reinterpret_cast<const uint4*>(job.values + (int64_t)(jj[q] >= 0 ? jj[q] : 0) * V);
+#pragma unroll
+        for (int h = 0; h < V / 8; ++h) v[q][h] = jj[q] >= 0 ? __ldg(src + h) : make_uint4(0u, 0u, 0u, 0u);
+    }
+    const int64_t mp = (int64_t)job.m_vec * V;
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+        const int k = ks * kBK + g * 8 + q;
+        if (k < job.K) {
+            uint4* dst = reinterpret_cast<uint4*>(job.at + (int64_t)k * mp + (int64_t)i * V);
+#pragma unroll
+            for (int h = 0; h < V / 8; ++h) dst[h] = v[q][h];
+        }
+    }
+}
+
 // ATMA = true: the A tiles come by TMA from a dense transposed copy of A (written by expand_group_kernel just
 // before; the loader warps then have nothing to do).  ATMA = false: the loader warps build them from the
 // compressed operand.
@@ -196,6 +274,7 @@ sspmm_fused_kernel(const __grid_constant__ Params gp) {
     volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(smem + L::kTmemPtrOff);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kAbortOff);
     volatile int* bcast = reinterpret_cast<volatile int*>(smem + L::kBcastOff);
+    volatile int* bcast2 = bcast + 1;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
@@ -295,13 +374,30 @@ sspmm_fused_kernel(const __grid_constant__ Params gp) {
                 const Problem* P = problem_of(it.prob);
                 if (gp.probs && it.prob != last_prob) {
                     fence_tensormap_acquire(&P->tmap_b);
-                    if (ATMA) fence_tensormap_acquire(&P->tmap_a);
+                    fence_tensormap_acquire(&P->tmap_b1);
+                    if constexpr (ATMA) {
+                        fence_tensormap_acquire(&P->tmap_a);
+                        // the dense copy of this product's A is written by loader warps of this and other CTAs
+                        const int need = P->expand_blocks;
+                        const int* done = gp.expand_state + 2 + it.prob;
+                        const long long t0 = clock64();
+                        while (ld_acquire_gpu(done) < need) {
+                            if (*abort_flag) { ok = false; break; }
+                            if (clock64() - t0 > g_wait_cycle_limit) {
+                                *abort_flag = 1;
+                                atomicCAS(&g_device_status, 0, kStatusWaitFused);
+                                ok = false;
+                                break;
+                            }
+                        }
+                        if (!ok) break;
+                        fence_proxy_async_all();      // those were ordinary stores; TMA reads through the async proxy
+                    }
                     last_prob = it.prob;
                 }
                 const int n0 = it.n_tile * BN;
                 const int wide = P->wide;
-                // a chunked request always brings the whole box (chunks past the matrix are zero-filled)
-                const int chunks = (wide & 1) ? BN / 64 : min(BN / 64, (P->N - n0 + 63) >> 6);
+                const int chunks = min(BN / 64, (P->N - n0 + 63) >> 6);
                 for (int ks = it.ks0; ks < it.ks1; ++ks) {
                     if (!mbar_wait(bar_b_empty + 8 * stage, phase ^ 1u, abort_flag, kStatusWaitFused)) { ok = false; break; }
                     const uint32_t full = bar_b_full + 8 * stage;
@@ -316,23 +412,15 @@ sspmm_fused_kernel(const __grid_constant__ Params gp) {
                         }
                     }
                     const uint32_t b_s = sbase + L::kBOff + stage * L::kBStage;
-                    if (wide & 1) {
+                    if ((wide & 1) && chunks == BN / 64) {
                         tma_load_3d(b_s, &P->tmap_b, 0, ks * kBK, n0 >> 6, full);
+                    } else if (wide & 1) {
+                        for (int c = 0; c < chunks; ++c) tma_load_3d(b_s + c * L::kChunk, &P->tmap_b1, 0, ks * kBK, (n0 >> 6) + c, full);
                     } else {
                         for (int c = 0; c < chunks; ++c) tma_load_3d(b_s + c * L::kChunk, &P->tmap_b, n0 + 64 * c, ks * kBK, 0, full);
                     }
                     if (++stage == BSTAGES) { stage = 0; phase ^= 1u; }
                     if ((ks & 7) == 7) publish(n + 1 + kPublishAhead, false);
-                }
-            }
-            // every CTA takes exactly one item past the end of the list; the CTA that does so last resets the queue
-            if (gp.dynamic) {
-                __threadfence();
-                const int done = atomicAdd(gp.queue + 1, 1);
-                if (done == (int)gridDim.x - 1) {
-                    gp.queue[0] = 0;
-                    gp.queue[1] = 0;
-                    __threadfence();
                 }
             }
         }
@@ -377,7 +465,34 @@ sspmm_fused_kernel(const __grid_constant__ Params gp) {
         }
       }
     } else if (warp >= kLoaderWarp0) {
-      if constexpr (!ATMA) {
+      if constexpr (ATMA) {
+        // ------------------------------------------------------------------ expansion (A tiles come by TMA)
+        // The 256 loader threads act as one block of the expansion: they take block numbers from a counter, write
+        // their part of a dense copy of A and count the block as done for its product.  They wait for nothing but
+        // each other, so the copies are always completed, whichever CTAs are resident.
+        if (gp.jobs) {
+            const int t = threadIdx.x - kLoaderWarp0 * 32;
+            constexpr int kExpandThreads = kLoaderGroups * kGroupThreads;
+            for (;;) {
+                if (t == 0) *bcast2 = atomicAdd(gp.expand_state, 1);
+                named_barrier_sync(3, kExpandThreads);
+                const int vb = *bcast2;
+                named_barrier_sync(3, kExpandThreads);            // everyone has read the number before the next one is written
+                if (vb >= gp.expand_blocks) break;
+                int lo = 0, hi = gp.n_jobs - 1;
+                while (lo < hi) {
+                    const int mid = (lo + hi + 1) >> 1;
+                    if (__ldg(&gp.jobs[mid].block_base) <= vb) lo = mid; else hi = mid - 1;
+                }
+                const ExpandJob job = gp.jobs[lo];
+                const int id = (vb - job.block_base) * kExpandThreads + t;
+                if (job.V == 16) expand_slots<16>(job, id); else expand_slots<8>(job, id);
+                __threadfence();
+                named_barrier_sync(3, kExpandThreads);
+                if (t == 0) atomicAdd(gp.expand_state + 2 + job.prob, 1);
+            }
+        }
+      } else {
         // ------------------------------------------------------------------ A loaders
         // The groups take the stages of the CTA's stage sequence in turn.  A stage goes through three steps,
         // each of which waits for memory: metadata, value vectors, shared-memory slot.  Under load a request
@@ -643,81 +758,17 @@ sspmm_fused_kernel(const __grid_constant__ Params gp) {
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, L::kTmemCols);
     }
-}
-
-// ---- expansion of the compressed operands of a group ---------------------------------------
-// At[k][i*V .. i*V+V) = value vector of vector row i at column k, or zeros; every element of At is written, so
-// nothing from an earlier run survives.  One thread per (vector row i, eight columns of a 64-column step): the
-// plan's metadata tells it which of its columns carry a vector and where, so a thread is two dependent reads
-// (metadata, value vectors) and its stores, with no shared memory and no barrier; consecutive threads have
-// consecutive i, so the stores of a warp to a row of At are contiguous.
-struct ExpandJob {
-    const uint4* meta;             // the plan's column masks, or null
-    const int* posmap;             // the plan's positions (when meta is null)
-    const __half* values;
-    __half* at;
-    int m_vec, K, V, k_steps;
-    int block_base;                // first thread block of this job
-};
-
-template <int V>
-__device__ __forceinline__ void expand_slots(const ExpandJob& job, int id) {
-    using A = ATile<V>;
-    const int i = id % job.m_vec;
-    const int g = (id / job.m_vec) & 7;
-    const int ks = id / (job.m_vec * 8);
-    if (ks >= job.k_steps) return;
-    const int tile = i / A::R, r = i % A::R;
-    const int64_t stage = (int64_t)tile * job.k_steps + ks;
-    int jj[8];
-    if (job.meta) {
-        const uint4 m = __ldg(job.meta + stage * A::R + r);
-        const unsigned long long mask = (unsigned long long)m.x | ((unsigned long long)m.y << 32);
-#pragma unroll
-        for (int q = 0; q < 8; ++q) {
-            const int kk = g * 8 + q;
-            jj[q] = ((mask >> kk) & 1ull) ? (int)m.z + __popcll(mask & ((1ull << kk) - 1ull)) : -1;
-        }
-    } else {
-#pragma unroll
-        for (int q = 0; q < 8; ++q) {
-            const int kk = g * 8 + q;
-            jj[q] = __ldg(job.posmap + (stage * kGroupThreads + r * A::TPR + kk % A::TPR) * A::SLOTS + kk / A::TPR);
+    // The CTA that leaves last puts the queue and the expansion counters back to zero for the next run.
+    if (threadIdx.x == 0 && gp.dynamic) {
+        __threadfence();
+        if (atomicAdd(gp.queue + 1, 1) == (int)gridDim.x - 1) {
+            gp.queue[0] = 0;
+            gp.queue[1] = 0;
+            if (gp.expand_state)
+                for (int i = 0; i < 2 + gp.n_jobs; ++i) gp.expand_state[i] = 0;
+            __threadfence();
         }
     }
-    uint4 v[8][V / 8];
-#pragma unroll
-    for (int q = 0; q < 8; ++q) {
-        const uint4* src = reinterpret_cast<const uint4*>(job.values + (int64_t)(jj[q] >= 0 ? jj[q] : 0) * V);
-#pragma unroll
-        for (int h = 0; h < V / 8; ++h) v[q][h] = jj[q] >= 0 ? __ldg(src + h) : make_uint4(0u, 0u, 0u, 0u);
-    }
-    const int64_t mp = (int64_t)job.m_vec * V;
-#pragma unroll
-    for (int q = 0; q < 8; ++q) {
-        const int k = ks * kBK + g * 8 + q;
-        if (k < job.K) {
-            uint4* dst = reinterpret_cast<uint4*>(job.at + (int64_t)k * mp + (int64_t)i * V);
-#pragma unroll
-            for (int h = 0; h < V / 8; ++h) dst[h] = v[q][h];
-        }
-    }
-}
-
-__global__ void __launch_bounds__(256)
-expand_group_kernel(const ExpandJob* __restrict__ jobs, int n_jobs) {
-    __shared__ ExpandJob job;
-    if (threadIdx.x == 0) {
-        int lo = 0, hi = n_jobs - 1;
-        while (lo < hi) {
-            const int mid = (lo + hi + 1) >> 1;
-            if (jobs[mid].block_base <= (int)blockIdx.x) lo = mid; else hi = mid - 1;
-        }
-        job = jobs[lo];
-    }
-    __syncthreads();
-    const int id = ((int)blockIdx.x - job.block_base) * 256 + (int)threadIdx.x;
-    if (job.V == 16) expand_slots<16>(job, id); else expand_slots<8>(job, id);
 }
 
 // ---- plan construction ------------------------------------------------------------------
@@ -860,11 +911,10 @@ struct sspmm_plan {
 struct sspmm_group {
     int device, count, BN;
     bool out_f16;
-    bool expanded;             // A tiles by TMA from dense transposed copies written by expand_group_kernel at every run
+    bool expanded;             // A tiles by TMA from dense transposed copies that the kernel's loader warps write at every run
     int n_items, grid;
     void* dev_block;           // one allocation: problems | items | queue | counters | expansion jobs | partials | copies of A
     fused::Params params;
-    const fused::ExpandJob* d_jobs;
     int expand_units;
     size_t scratch_bytes;      // partial tiles + copies of A
 };
@@ -915,7 +965,8 @@ bool fill_problem(Problem* P, const sspmm_plan* plan, const void* values, const 
     }
     const int Mp = plan->m_vec * plan->V;
     const size_t oes = out_f16 ? 2 : 4;
-    P->wide = (N % 64 == 0 && encode_chunked(enc, &P->tmap_b, rhs, (uint64_t)N, (uint64_t)plan->K, (uint32_t)(BN / 64))) ? 1 : 0;
+    P->wide = (N % 64 == 0 && encode_chunked(enc, &P->tmap_b, rhs, (uint64_t)N, (uint64_t)plan->K, (uint32_t)(BN / 64)) &&
+               encode_chunked(enc, &P->tmap_b1, rhs, (uint64_t)N, (uint64_t)plan->K, 1)) ? 1 : 0;
     if ((!P->wide && !encode_map(enc, &P->tmap_b, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, rhs, (uint64_t)N, (uint64_t)plan->K, 64, 64,
                                  CU_TENSOR_MAP_SWIZZLE_128B)) ||
         !encode_map(enc, &P->tmap_c, out_f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, oes, out,
@@ -923,10 +974,11 @@ bool fill_problem(Problem* P, const sspmm_plan* plan, const void* values, const 
         set_error("cuTensorMapEncodeTiled failed (Mp=%d N=%d K=%d)", Mp, N, plan->K);
         return false;
     }
+    if (!P->wide) P->tmap_b1 = P->tmap_b;       // never used then; kept valid
     P->meta = plan->meta; P->posmap = plan->posmap;
     P->values = static_cast<const __half*>(values); P->out = out;
     P->Mp = Mp; P->N = N; P->K = plan->K; P->V = plan->V;
-    P->k_steps = plan->k_steps; P->m_tiles = plan->m_tiles; P->n_tiles = (N + BN - 1) / BN;
+    P->k_steps = plan->k_steps; P->m_tiles = plan->m_tiles; P->n_tiles = (N + BN - 1) / BN; P->expand_blocks = 0;
     return true;
 }
 
@@ -1072,6 +1124,7 @@ int sspmm_planned(const sspmm_plan* plan, const void* values_f16, const void* rh
     while (BN > 64 && (int64_t)plan->m_tiles * ((N + BN - 1) / BN) < sms) BN >>= 1;
     fused::Params p;
     p.probs = nullptr; p.items = nullptr; p.dynamic = 0; p.queue = nullptr; p.partials = nullptr; p.counters = nullptr;
+    p.jobs = nullptr; p.n_jobs = 0; p.expand_blocks = 0; p.expand_state = nullptr;
     if (!fused::fill_problem(&p.inline_prob, plan, values_f16, rhs_f16, out, N, out_is_f16 != 0, BN)) return (int)cudaErrorInvalidValue;
     const int64_t tiles = (int64_t)p.inline_prob.m_tiles * p.inline_prob.n_tiles;
     if (tiles > 0x7fffffffLL) { set_error("problem too large for 32-bit tile ids"); return (int)cudaErrorInvalidValue; }
@@ -1177,14 +1230,15 @@ int sspmm_group_create(const sspmm_group_item* items, int count, int out_is_f16,
             j.meta = pl->meta; j.posmap = pl->posmap;
             j.values = static_cast<const __half*>(items[i].values_f16); j.at = nullptr;
             j.m_vec = pl->m_vec; j.K = pl->K; j.V = pl->V; j.k_steps = pl->k_steps;
-            j.block_base = g->expand_units;
-            g->expand_units += (int)(((int64_t)pl->m_vec * 8 * pl->k_steps + 255) / 256);
+            j.prob = i;
+            probs[i].expand_blocks = (int)(((int64_t)pl->m_vec * 8 * pl->k_steps + 255) / 256);
         }
     }
     const size_t off_items = up(probs.size() * sizeof(fused::Problem));
     const size_t off_queue = off_items + up(list.size() * sizeof(fused::Item));
     const size_t off_counters = off_queue + 256;
-    const size_t off_jobs = off_counters + up((size_t)(cslots + 1) * sizeof(int));
+    const size_t off_state = off_counters + up((size_t)(cslots + 1) * sizeof(int));
+    const size_t off_jobs = off_state + up((size_t)(count + 2) * sizeof(int));
     const size_t off_partials = off_jobs + up(jobs.size() * sizeof(fused::ExpandJob));
     const size_t partial_bytes = up((size_t)pslots * fused::kBM * BN * sizeof(float));
     const size_t off_at = off_partials + partial_bytes;
@@ -1206,7 +1260,16 @@ int sspmm_group_create(const sspmm_group_item* items, int count, int out_is_f16,
             maps_ok = enc && fused::encode_map(enc, &probs[i].tmap_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, jobs[i].at,
                                                (uint64_t)probs[i].Mp, (uint64_t)probs[i].K, 64, 64, CU_TENSOR_MAP_SWIZZLE_128B);
         }
-        if (maps_ok) e = cudaMemcpy(base + off_jobs, jobs.data(), jobs.size() * sizeof(fused::ExpandJob), cudaMemcpyHostToDevice);
+        // the copies are written in the order the products are multiplied (longest K first)
+        std::vector<fused::ExpandJob> sorted;
+        sorted.reserve((size_t)count);
+        for (int oi = 0; oi < count; ++oi) {
+            fused::ExpandJob j = jobs[order[oi]];
+            j.block_base = g->expand_units;
+            g->expand_units += probs[order[oi]].expand_blocks;
+            sorted.push_back(j);
+        }
+        if (maps_ok) e = cudaMemcpy(base + off_jobs, sorted.data(), sorted.size() * sizeof(fused::ExpandJob), cudaMemcpyHostToDevice);
     }
     if (e == cudaSuccess) e = cudaMemcpy(base, probs.data(), probs.size() * sizeof(fused::Problem), cudaMemcpyHostToDevice);
     if (e == cudaSuccess) e = cudaMemcpy(base + off_items, list.data(), list.size() * sizeof(fused::Item), cudaMemcpyHostToDevice);
@@ -1230,7 +1293,10 @@ int sspmm_group_create(const sspmm_group_item* items, int count, int out_is_f16,
     g->params.queue = reinterpret_cast<int*>(base + off_queue);
     g->params.counters = reinterpret_cast<int*>(base + off_counters);
     g->params.partials = reinterpret_cast<float*>(base + off_partials);
-    g->d_jobs = reinterpret_cast<const fused::ExpandJob*>(base + off_jobs);
+    g->params.jobs = g->expanded ? reinterpret_cast<const fused::ExpandJob*>(base + off_jobs) : nullptr;
+    g->params.n_jobs = g->expanded ? count : 0;
+    g->params.expand_blocks = g->expand_units;
+    g->params.expand_state = g->expanded ? reinterpret_cast<int*>(base + off_state) : nullptr;
     *group = g;
     return 0;
 }
@@ -1239,11 +1305,6 @@ int sspmm_group_run(sspmm_group* group, void* stream) {
     set_error("%s", "");
     if (!group) { set_error("null group"); return (int)cudaErrorInvalidValue; }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    if (group->expanded) {
-        fused::expand_group_kernel<<<group->expand_units, 256, 0, st>>>(group->d_jobs, group->count);
-        cudaError_t e0 = cudaGetLastError();
-        if (e0 != cudaSuccess) { set_error("group expansion launch: %s", cudaGetErrorString(e0)); return (int)e0; }
-    }
     cudaError_t e = fused::launch(group->params, group->BN, group->out_f16, group->expanded, group->grid, st);
     if (e != cudaSuccess) { set_error("group launch: %s", cudaGetErrorString(e)); return (int)e; }
     return 0;
@@ -1255,7 +1316,7 @@ int sspmm_group_info(const sspmm_group* group, int* tile_columns, int* work_item
     if (tile_columns) *tile_columns = group->BN;
     if (work_items) *work_items = group->n_items;
     if (ctas) *ctas = group->grid;
-    if (launches) *launches = group->expanded ? 2 : 1;
+    if (launches) *launches = 1;
     if (scratch_bytes) *scratch_bytes = (int64_t)group->scratch_bytes;
     return 0;
 }
