@@ -156,13 +156,21 @@ int sspmm_planned(const sspmm_plan* plan, const void* values_f16, const void* rh
  * form one work list, longest first, taken by the CTAs from a shared queue, so that small products
  * fill the SMs a large one leaves idle; tiles with a long K range are cut into parts whose fp32
  * partial tiles are added, in part order, by whichever part finishes last.
- * mode 1 (compressed): the A tiles are built inside the kernel from the compressed operand; one
- *     launch per run and no scratch for A;
- * mode 2 (expanded): every run first writes dense transposed copies of the A operands (one extra
- *     launch for the whole group, K * m_vec*V * 2 bytes per product, owned by the group) and the
- *     tensor-core kernel fetches its A tiles from them by TMA: about a third less time per K step,
- *     which pays off once every SM has a few dozen K steps of work;
- * mode 0: chosen from the amount of work per SM.
+ * Every mode is ONE launch per run.
+ * mode 1 (compressed): the A tiles are built inside the kernel from the compressed operand, in
+ *     registers, by eight loader warps per CTA; no scratch for A;
+ * mode 2 (expanded): the loader warps of all CTAs first write dense transposed copies of the A
+ *     operands (K * m_vec*V * 2 bytes per product, owned by the group), block by block and in the
+ *     order the products are multiplied, while the other warps already multiply; the tensor-core
+ *     warps fetch their A tiles from the copies by TMA once a product's copy is complete.  About a
+ *     quarter less time per K step, which pays off once every SM has a few dozen K steps of work;
+ * mode 3 (expanded, CTA pairs): as mode 2 with tiles of 256 rows x 256 columns computed by two
+ *     CTAs of a cluster (tcgen05 cta_group::2, each CTA fetching its own 128 rows of A and half of
+ *     the B tile).  Measured no faster than mode 2 on the conv workload (products with fewer than
+ *     256 rows pay for the padding), so never chosen automatically;
+ * mode 0: 1 or 2, chosen from the amount of work per SM.
+ * Products of one group that multiply the same dense operand (same rhs pointer, N and K) are
+ * scheduled panel by panel, so that a column panel of B is fetched from HBM once for all of them.
  * sspmm_group_create allocates the descriptors and the scratch once (and synchronises);
  * sspmm_group_run allocates nothing and does not synchronise.  Operand pointers are fixed at
  * creation; the contents of every operand, the values included, may change between runs.  A group
@@ -179,7 +187,7 @@ typedef struct sspmm_group_item {
 } sspmm_group_item;
 int sspmm_group_create(const sspmm_group_item* items, int count, int out_is_f16, int mode, sspmm_group** group);
 int sspmm_group_run(sspmm_group* group, void* stream);
-/* Any output pointer may be NULL.  launches = kernels per run (1 or 2). */
+/* Any output pointer may be NULL.  launches = kernels per run (always 1). */
 int sspmm_group_info(const sspmm_group* group, int* tile_columns, int* work_items, int* ctas, int* launches,
                      int64_t* scratch_bytes);
 int sspmm_group_destroy(sspmm_group* group);

@@ -5,6 +5,7 @@
 #include "sspmm_simt.cu"
 #include "sspmm_block.cu"
 #include "sspmm_fused.cu"
+#include "sspmm_fused_pair.cu"
 #include "svc.cu"
 #include "c_api.cu"
 #include "cxx_api.cu"

@@ -64,7 +64,7 @@ constexpr int kRing = 32;
 struct alignas(64) Problem {
     CUtensorMap tmap_a;        // expanded mode only: At {M', K, 1} fp16 (dense transposed copy of A), box 64 x 64, 128-byte swizzle
     CUtensorMap tmap_b;        // B  {N, K, 1}   fp16, box 64 x 64, 128-byte swizzle (or the chunked view, see `wide`)
-    CUtensorMap tmap_b1;       // chunked view of B with a one-chunk box: the last, partly filled column tile fetches only its own chunks
+    CUtensorMap tmap_b1;       // B {N, K, 1}, box 64 x 64 at any column that is a multiple of 8: the last, partly filled column tile fetches only its own chunks
     CUtensorMap tmap_c;        // C  {N, M', 1}  fp16/fp32, box (64 bytes) x 128 rows, 64-byte swizzle
     const uint4* meta;         // plan, ascending rows: [m_tile][k_step][row in tile] {mask lo, mask hi, start, 0}
     const int* posmap;         // plan, other structures: [m_tile][k_step][loader thread][slot] index of the vector or -1
@@ -415,7 +415,7 @@ sspmm_fused_kernel(const __grid_constant__ Params gp) {
                     if ((wide & 1) && chunks == BN / 64) {
                         tma_load_3d(b_s, &P->tmap_b, 0, ks * kBK, n0 >> 6, full);
                     } else if (wide & 1) {
-                        for (int c = 0; c < chunks; ++c) tma_load_3d(b_s + c * L::kChunk, &P->tmap_b1, 0, ks * kBK, (n0 >> 6) + c, full);
+                        for (int c = 0; c < chunks; ++c) tma_load_3d(b_s + c * L::kChunk, &P->tmap_b1, n0 + 64 * c, ks * kBK, 0, full);
                     } else {
                         for (int c = 0; c < chunks; ++c) tma_load_3d(b_s + c * L::kChunk, &P->tmap_b, n0 + 64 * c, ks * kBK, 0, full);
                     }
@@ -911,6 +911,7 @@ struct sspmm_plan {
 struct sspmm_group {
     int device, count, BN;
     bool out_f16;
+    bool pair;                 // CTA-pair kernel (tiles of 256 x 256); always expanded
     bool expanded;             // A tiles by TMA from dense transposed copies that the kernel's loader warps write at every run
     int n_items, grid;
     void* dev_block;           // one allocation: problems | items | queue | counters | expansion jobs | partials | copies of A
@@ -948,6 +949,10 @@ cudaError_t launch_bn(const Params& p, int BN, int grid, cudaStream_t st, bool s
     return launch_typed<64, 8, OutT, ATMA>(p, grid, st, setup_only);
 }
 
+// CTA-pair kernel (sspmm_fused_pair.cu)
+cudaError_t launch_pair(const Params& p, bool out_f16, int pairs, cudaStream_t st, bool setup_only);
+constexpr bool kAutoPairs = false;
+
 cudaError_t launch(const Params& p, int BN, bool out_f16, bool a_tma, int grid, cudaStream_t st, bool setup_only = false) {
     if (a_tma) return out_f16 ? launch_bn<__half, true>(p, BN, grid, st, setup_only) : launch_bn<float, true>(p, BN, grid, st, setup_only);
     return out_f16 ? launch_bn<__half, false>(p, BN, grid, st, setup_only) : launch_bn<float, false>(p, BN, grid, st, setup_only);
@@ -955,7 +960,7 @@ cudaError_t launch(const Params& p, int BN, bool out_f16, bool a_tma, int grid, 
 
 // Fills everything of a Problem but nothing that lives on the device.  Returns false with the error set.
 bool fill_problem(Problem* P, const sspmm_plan* plan, const void* values, const void* rhs, void* out, int N, bool out_f16,
-                  int BN) {
+                  int BN, bool pair = false) {
     EncodeFn enc = encode_fn();
     if (!enc) { set_error("cuTensorMapEncodeTiled is not available from the CUDA driver"); return false; }
     if (!plan || !plan->fused) { set_error("the plan does not support the one-launch kernel"); return false; }
@@ -965,20 +970,21 @@ bool fill_problem(Problem* P, const sspmm_plan* plan, const void* values, const 
     }
     const int Mp = plan->m_vec * plan->V;
     const size_t oes = out_f16 ? 2 : 4;
-    P->wide = (N % 64 == 0 && encode_chunked(enc, &P->tmap_b, rhs, (uint64_t)N, (uint64_t)plan->K, (uint32_t)(BN / 64)) &&
-               encode_chunked(enc, &P->tmap_b1, rhs, (uint64_t)N, (uint64_t)plan->K, 1)) ? 1 : 0;
-    if ((!P->wide && !encode_map(enc, &P->tmap_b, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, rhs, (uint64_t)N, (uint64_t)plan->K, 64, 64,
+    // a CTA pair fetches the B tile in two halves, one per CTA
+    P->wide = (N % 64 == 0 && encode_chunked(enc, &P->tmap_b, rhs, (uint64_t)N, (uint64_t)plan->K, (uint32_t)(pair ? BN / 128 : BN / 64))) ? 1 : 0;
+    if (!encode_map(enc, &P->tmap_b1, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, rhs, (uint64_t)N, (uint64_t)plan->K, 64, 64,
+                    CU_TENSOR_MAP_SWIZZLE_128B) ||
+        (!P->wide && !encode_map(enc, &P->tmap_b, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, rhs, (uint64_t)N, (uint64_t)plan->K, 64, 64,
                                  CU_TENSOR_MAP_SWIZZLE_128B)) ||
         !encode_map(enc, &P->tmap_c, out_f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, oes, out,
                     (uint64_t)N, (uint64_t)Mp, (uint32_t)(64 / oes), 128, CU_TENSOR_MAP_SWIZZLE_64B)) {
         set_error("cuTensorMapEncodeTiled failed (Mp=%d N=%d K=%d)", Mp, N, plan->K);
         return false;
     }
-    if (!P->wide) P->tmap_b1 = P->tmap_b;       // never used then; kept valid
     P->meta = plan->meta; P->posmap = plan->posmap;
     P->values = static_cast<const __half*>(values); P->out = out;
     P->Mp = Mp; P->N = N; P->K = plan->K; P->V = plan->V;
-    P->k_steps = plan->k_steps; P->m_tiles = plan->m_tiles; P->n_tiles = (N + BN - 1) / BN; P->expand_blocks = 0;
+    P->k_steps = plan->k_steps; P->m_tiles = pair ? (plan->m_tiles + 1) / 2 : plan->m_tiles; P->n_tiles = (N + BN - 1) / BN; P->expand_blocks = 0;
     return true;
 }
 
@@ -1141,7 +1147,7 @@ int sspmm_group_create(const sspmm_group_item* items, int count, int out_is_f16,
     if (!group) { set_error("null output pointer"); return (int)cudaErrorInvalidValue; }
     *group = nullptr;
     if (!items || count <= 0) { set_error("a group needs at least one product"); return (int)cudaErrorInvalidValue; }
-    if (mode < 0 || mode > 2) { set_error("group mode must be 0 (automatic), 1 (compressed) or 2 (expanded)"); return (int)cudaErrorInvalidValue; }
+    if (mode < 0 || mode > 3) { set_error("group mode must be 0 (automatic), 1 (compressed), 2 (expanded) or 3 (expanded, CTA pairs)"); return (int)cudaErrorInvalidValue; }
     const int sms = current_device_sm_count();
     if (sms <= 0) return (int)cudaErrorNoDevice;
     int dev = 0;
@@ -1159,12 +1165,23 @@ int sspmm_group_create(const sspmm_group_item* items, int count, int out_is_f16,
         for (int i = 0; i < count; ++i) tiles += (int64_t)items[i].plan->m_tiles * ((items[i].N + BN - 1) / BN);
         if (tiles >= 2 * sms || BN == 64) break;
     }
+    // CTA pairs (tiles of 256 x 256, see sspmm_fused_pair.cu) when asked for, or when the group is large enough for
+    // 256-column tiles and for the expanded mode
+    bool pair = mode == 3;
+    if (mode == 0 && BN == 256 && fused::kAutoPairs) {
+        double est = 0;
+        for (int i = 0; i < count; ++i)
+            est += (double)items[i].plan->m_tiles * ((items[i].N + 255) / 256) * (items[i].plan->k_steps + 2);
+        pair = est / sms >= 48.0;
+    }
+    if (pair) BN = 256;
+    const int units = pair ? sms / 2 : sms;            // what holds one tile: an SM, or a pair of SMs
     std::vector<fused::Problem> probs((size_t)count);
     int64_t tiles = 0;
     double work = 0;                                   // K steps, with a fixed cost of two steps per tile
     for (int i = 0; i < count; ++i) {
         if (!fused::fill_problem(&probs[i], items[i].plan, items[i].values_f16, items[i].rhs_f16, items[i].out, items[i].N,
-                                 out_is_f16 != 0, BN))
+                                 out_is_f16 != 0, BN, pair))
             return (int)cudaErrorInvalidValue;
         const int64_t t = (int64_t)probs[i].m_tiles * probs[i].n_tiles;
         tiles += t;
@@ -1173,34 +1190,51 @@ int sspmm_group_create(const sspmm_group_item* items, int count, int out_is_f16,
     if (tiles > (1 << 26)) { set_error("group too large (%lld tiles)", (long long)tiles); return (int)cudaErrorInvalidValue; }
     // Tiles longer than `cut` K steps are cut into parts so that no single item is a large share of an
     // SM's work; the parts' fp32 partial tiles are summed by whichever part finishes last.
-    const double per_sm = work / sms;
+    const double per_sm = work / units;
     int cut = (int)(per_sm / 3.0);
     if (cut < 8) cut = 8;
     std::vector<fused::Item> list;
     list.reserve((size_t)tiles + 1024);
     int pslots = 0, cslots = 0;
-    // longest items first (a greedy queue then balances itself); inside a product, tiles that share a panel of B
-    // (same n tile) are neighbours, so CTAs running side by side reuse it from L2
+    // longest items first (a greedy queue then balances itself).  Products that multiply the same dense operand
+    // (same pointer, width and depth) form a bundle whose tiles are emitted panel by panel: all tiles of all
+    // bundle members that read one column panel of B are neighbours in the list, so CTAs running side by side
+    // fetch the panel from HBM once and from L2 afterwards.
     std::vector<int> order((size_t)count);
     for (int i = 0; i < count; ++i) order[i] = i;
     std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return probs[a].k_steps > probs[b].k_steps; });
+    std::vector<char> placed((size_t)count, 0);
     for (int oi = 0; oi < count; ++oi) {
-        const int i = order[oi];
-        const fused::Problem& P = probs[i];
-        int parts = (tiles < 8 * (int64_t)sms && P.k_steps > cut) ? (P.k_steps + cut - 1) / cut : 1;
+        if (placed[(size_t)order[oi]]) continue;
+        const int lead = order[oi];
+        std::vector<int> bundle;
+        for (int oj = oi; oj < count; ++oj) {
+            const int j = order[oj];
+            if (placed[(size_t)j]) continue;
+            if (items[j].rhs_f16 == items[lead].rhs_f16 && items[j].N == items[lead].N && probs[j].K == probs[lead].K &&
+                probs[j].k_steps == probs[lead].k_steps && probs[j].n_tiles == probs[lead].n_tiles) {
+                bundle.push_back(j);
+                placed[(size_t)j] = 1;
+            }
+        }
+        const fused::Problem& L = probs[lead];
+        int parts = (tiles < 8 * (int64_t)units && L.k_steps > cut) ? (L.k_steps + cut - 1) / cut : 1;
         if (parts > 16) parts = 16;
-        const int sps = (P.k_steps + parts - 1) / parts;
-        parts = (P.k_steps + sps - 1) / sps;
-        for (int nt = 0; nt < P.n_tiles; ++nt)
-            for (int mt = 0; mt < P.m_tiles; ++mt) {
-                if (parts == 1) {
-                    list.push_back(fused::Item{i, mt, nt, 0, P.k_steps, 0, 1 << 8, 0});
-                } else {
-                    for (int z = 0; z < parts; ++z)
-                        list.push_back(fused::Item{i, mt, nt, z * sps, std::min(P.k_steps, (z + 1) * sps), pslots + z,
-                                                   z | (parts << 8), cslots});
-                    pslots += parts;
-                    ++cslots;
+        const int sps = (L.k_steps + parts - 1) / parts;
+        parts = (L.k_steps + sps - 1) / sps;
+        for (int nt = 0; nt < L.n_tiles; ++nt)
+            for (int i : bundle) {
+                const fused::Problem& P = probs[i];
+                for (int mt = 0; mt < P.m_tiles; ++mt) {
+                    if (parts == 1) {
+                        list.push_back(fused::Item{i, mt, nt, 0, P.k_steps, 0, 1 << 8, 0});
+                    } else {
+                        for (int z = 0; z < parts; ++z)
+                            list.push_back(fused::Item{i, mt, nt, z * sps, std::min(P.k_steps, (z + 1) * sps), pslots + z,
+                                                       z | (parts << 8), cslots});
+                        pslots += parts;
+                        ++cslots;
+                    }
                 }
             }
     }
@@ -1210,11 +1244,12 @@ int sspmm_group_create(const sspmm_group_item* items, int count, int out_is_f16,
     if (!g) return (int)cudaErrorMemoryAllocation;
     g->device = dev; g->count = count; g->BN = BN; g->out_f16 = out_is_f16 != 0;
     g->n_items = (int)list.size();
-    g->grid = g->n_items < sms ? g->n_items : sms;
+    g->grid = g->n_items < units ? g->n_items : units;  // CTAs, or CTA pairs
+    g->pair = pair;
     // Measured on B200: with the A tiles built by the loader warps a K step takes about 1150 cycles, with A tiles
     // fetched by TMA from a dense copy about 700-750; writing the copies costs one more launch and a few tens of
     // microseconds.  So groups with much work per SM expand, small ones (latency matters) do not.
-    g->expanded = mode == 2 || (mode == 0 && per_sm >= 48.0);
+    g->expanded = pair || mode == 2 || (mode == 0 && per_sm >= 48.0);
     auto up = [](size_t x) { return (x + 255) & ~(size_t)255; };
     std::vector<fused::ExpandJob> jobs;
     std::vector<size_t> at_off((size_t)count, 0);
@@ -1237,10 +1272,10 @@ int sspmm_group_create(const sspmm_group_item* items, int count, int out_is_f16,
     const size_t off_items = up(probs.size() * sizeof(fused::Problem));
     const size_t off_queue = off_items + up(list.size() * sizeof(fused::Item));
     const size_t off_counters = off_queue + 256;
-    const size_t off_state = off_counters + up((size_t)(cslots + 1) * sizeof(int));
+    const size_t off_state = off_counters + up((size_t)(2 * cslots + 2) * sizeof(int));
     const size_t off_jobs = off_state + up((size_t)(count + 2) * sizeof(int));
     const size_t off_partials = off_jobs + up(jobs.size() * sizeof(fused::ExpandJob));
-    const size_t partial_bytes = up((size_t)pslots * fused::kBM * BN * sizeof(float));
+    const size_t partial_bytes = up((size_t)pslots * (pair ? 2 : 1) * fused::kBM * BN * sizeof(float));
     const size_t off_at = off_partials + partial_bytes;
     g->scratch_bytes = partial_bytes + at_bytes;
     const size_t total = off_at + at_bytes;
@@ -1273,7 +1308,8 @@ int sspmm_group_create(const sspmm_group_item* items, int count, int out_is_f16,
     }
     if (e == cudaSuccess) e = cudaMemcpy(base, probs.data(), probs.size() * sizeof(fused::Problem), cudaMemcpyHostToDevice);
     if (e == cudaSuccess) e = cudaMemcpy(base + off_items, list.data(), list.size() * sizeof(fused::Item), cudaMemcpyHostToDevice);
-    if (e == cudaSuccess) e = fused::launch(g->params, BN, g->out_f16, g->expanded, 1, nullptr, true);
+    if (e == cudaSuccess) e = pair ? fused::launch_pair(g->params, g->out_f16, 1, nullptr, true)
+                                   : fused::launch(g->params, BN, g->out_f16, g->expanded, 1, nullptr, true);
     if (e == cudaSuccess && !maps_ok) {
         cudaFree(g->dev_block);
         delete g;
@@ -1305,7 +1341,8 @@ int sspmm_group_run(sspmm_group* group, void* stream) {
     set_error("%s", "");
     if (!group) { set_error("null group"); return (int)cudaErrorInvalidValue; }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    cudaError_t e = fused::launch(group->params, group->BN, group->out_f16, group->expanded, group->grid, st);
+    cudaError_t e = group->pair ? fused::launch_pair(group->params, group->out_f16, group->grid, st, false)
+                                : fused::launch(group->params, group->BN, group->out_f16, group->expanded, group->grid, st);
     if (e != cudaSuccess) { set_error("group launch: %s", cudaGetErrorString(e)); return (int)e; }
     return 0;
 }
@@ -1315,7 +1352,7 @@ int sspmm_group_info(const sspmm_group* group, int* tile_columns, int* work_item
     if (!group) return (int)cudaErrorInvalidValue;
     if (tile_columns) *tile_columns = group->BN;
     if (work_items) *work_items = group->n_items;
-    if (ctas) *ctas = group->grid;
+    if (ctas) *ctas = group->pair ? 2 * group->grid : group->grid;
     if (launches) *launches = 1;
     if (scratch_bytes) *scratch_bytes = (int64_t)group->scratch_bytes;
     return 0;

@@ -221,7 +221,7 @@ class Group:
     ``mode``: COMPRESSED builds the A tiles inside the kernel (one launch, no scratch for A), EXPANDED writes dense
     copies of A first (two launches, faster per K step), AUTO picks by the work per SM."""
 
-    AUTO, COMPRESSED, EXPANDED = 0, 1, 2
+    AUTO, COMPRESSED, EXPANDED, PAIRS = 0, 1, 2, 3
 
     def __init__(self, products, mode: int = 0):
         import ctypes as C

@@ -50,7 +50,8 @@ def test_ffn_v16_planned_and_grouped(lib, shape_id, sparsity_id):
     assert_close(got, ref)
     if plan.one_launch:
         d_val, d_rhs = dev(vals, rhs)
-        for dt, mode in ((torch.float16, ops.Group.COMPRESSED), (torch.float32, ops.Group.COMPRESSED), (torch.float16, ops.Group.EXPANDED)):
+        for dt, mode in ((torch.float16, ops.Group.COMPRESSED), (torch.float32, ops.Group.COMPRESSED), (torch.float16, ops.Group.EXPANDED),
+                         (torch.float16, ops.Group.PAIRS), (torch.float32, ops.Group.PAIRS)):
             out = torch.full((a.M, rhs.shape[1]), float("nan"), dtype=dt, device=DEV)
             g = ops.Group([(plan, d_val, d_rhs, out)], mode=mode)
             assert g.launches == 1
@@ -95,7 +96,7 @@ def test_irregular_structure_falls_back(lib):
         ops.Group([(plan, d_val, d_rhs, torch.empty((16, 64), dtype=torch.float16, device=DEV))])
 
 
-@pytest.mark.parametrize("mode", [ops.Group.COMPRESSED, ops.Group.EXPANDED])
+@pytest.mark.parametrize("mode", [ops.Group.COMPRESSED, ops.Group.EXPANDED, ops.Group.PAIRS])
 def test_group_of_mixed_products(lib, mode):
     """Products of different shapes, V = 8 and 16, K from 64 to 2304, column counts with partial tiles, in one
     group (A tiles built in the kernel, or fetched from dense copies written at every run); every product against
@@ -148,13 +149,17 @@ def test_conv_layer_planned_wide(lib, N):
     out2 = torch.full_like(got, float("nan"))
     g = ops.Group([(plan, d_val, d_rhs, out)], mode=ops.Group.COMPRESSED)
     g2 = ops.Group([(plan, d_val, d_rhs, out2)], mode=ops.Group.EXPANDED)
+    out3 = torch.full_like(got, float("nan"))
+    g3 = ops.Group([(plan, d_val, d_rhs, out3)], mode=ops.Group.PAIRS)
     g.run()
     g2.run()
+    g3.run()
     torch.cuda.synchronize()
     assert ops.device_status() == 0
     a_np, b_np = got.float().cpu().numpy(), out.float().cpu().numpy()
     assert_close(b_np, a_np)
     assert_close(out2.float().cpu().numpy(), a_np)
+    assert_close(out3.float().cpu().numpy(), a_np)
     for rows in ((0, 2), (15, 17), (a.M // V - 2, a.M // V)):
         ref = spmm_oracle.sspmm_host(V, ptr, col, vals, rhs, rows=rows, threads=8)
         assert_close(a_np[rows[0] * V: rows[1] * V], ref)
