@@ -207,8 +207,11 @@ static int spmm_entry(int m_vec, int V, int N, int K, int batch, const int* row_
         if (ex.query) { *ex.query = bytes; return 0; }
         void* scratch = nullptr;
         if (ex.caller_workspace) {
-            if (bytes > ex.workspace_bytes) { chunk = 0; cap = 0; bytes = 0; }     // too small: long rows are not split (slower, same result)
-            else scratch = ex.workspace;
+            if (bytes > ex.workspace_bytes) {          // too small: long rows are not split (slower, same result)
+                chunk = 0; cap = 0;
+                bytes = (ex.workspace && ex.workspace_bytes >= 16) ? 16 : 0;     // the work counter alone still fits
+            }
+            if (bytes) scratch = ex.workspace;
         } else if (bytes) {
             keep_pool_memory();
             e = cudaMallocAsync(&scratch, bytes, st);
