@@ -252,7 +252,7 @@ struct svc_job {
     bool with_values;
     long long nvec;
     long long table_ints;
-    long long class_groups[6];
+    long long class_groups[kSvcClasses];
     int device;
     cudaStream_t stream;
 };
@@ -391,10 +391,11 @@ int svc_begin(int M, int K, int vec_length, const int* d_csr_row_ptr, const int*
     j->p.vals = static_cast<const __half*>(d_csr_values_f16);
     j->with_values = d_csr_values_f16 != nullptr;
     const size_t mv = (size_t)j->p.m_vec;
-    // one allocation: vec_ptr[mv+1] | mode[mv] | tbl_len[mv] | pad | tbl_off[mv+1] | totals[2]
-    const size_t ints = (mv + 1) + mv + mv;
+    // one allocation: vec_ptr[mv+1] | mode[mv] | tbl_len[mv] | class_list[mv] | queue[8] | pad | tbl_off[mv+1] | totals
+    const size_t ints = (mv + 1) + mv + mv + mv + 8;
     const size_t ints_padded = (ints + 3) & ~(size_t)3;
-    const size_t bytes = ints_padded * 4 + (mv + 1 + kSvcTotals) * 8;
+    const size_t scan_blocks = (size_t)svc_scan_blocks((long long)mv);
+    const size_t bytes = ints_padded * 4 + (mv + 1 + kSvcTotals + scan_blocks * kSvcScanFields) * 8;
     void* base = nullptr;
     keep_pool_memory();
     cudaError_t e = cudaMallocAsync(&base, bytes, st);
@@ -402,14 +403,17 @@ int svc_begin(int M, int K, int vec_length, const int* d_csr_row_ptr, const int*
     j->s.vec_ptr = static_cast<int*>(base);
     j->s.mode = j->s.vec_ptr + mv + 1;
     j->s.tbl_len = j->s.mode + mv;
+    j->s.class_list = j->s.tbl_len + mv;
+    j->s.queue = j->s.class_list + mv;
     j->s.tbl_off = reinterpret_cast<long long*>(static_cast<int*>(base) + ints_padded);
     j->s.totals = j->s.tbl_off + mv + 1;
+    j->s.block_sums = j->s.totals + kSvcTotals;
     j->s.tables = nullptr;
     e = svc_count_and_scan(j->p, j->s, j->with_values, st);
     long long totals[kSvcTotals] = {0};
     if (e == cudaSuccess) e = cudaMemcpyAsync(totals, j->s.totals, sizeof totals, cudaMemcpyDeviceToHost, st);
     if (e == cudaSuccess) e = cudaStreamSynchronize(st);
-    const int bad = (int)totals[8];
+    const int bad = (int)totals[2 + kSvcClasses];
     if (e != cudaSuccess || bad || totals[0] > 0x7fffffffLL) {
         cudaFreeAsync(base, st);
         delete j;
@@ -420,7 +424,7 @@ int svc_begin(int M, int K, int vec_length, const int* d_csr_row_ptr, const int*
     }
     j->nvec = totals[0];
     j->table_ints = totals[1];
-    for (int c = 0; c < 6; ++c) j->class_groups[c] = totals[2 + c];
+    for (int c = 0; c < kSvcClasses; ++c) j->class_groups[c] = totals[2 + c];
     *nvec = totals[0];
     *job = j;
     return 0;
@@ -587,7 +591,7 @@ int svc_replayed_rows(svc_job* j, int64_t* rows) {
     g_err[0] = 0;
     if (!j || !rows) return (int)cudaErrorInvalidValue;
     *rows = 0;
-    for (int c = 1; c < 6; ++c) *rows += j->class_groups[c];       // every class but "ascending"
+    for (int c = 1; c < kSvcClasses; ++c) *rows += j->class_groups[c];       // every class but "ascending"
     return 0;
 }
 

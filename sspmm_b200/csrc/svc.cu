@@ -19,7 +19,7 @@
 //                      already the exact answer: it is when the largest column id
 //                      is below the final table length (every key then sits in its
 //                      home slot).
-//   svc_scan_kernel    exclusive scans (vector row pointers, scratch offsets) and a
+//   svc_scan_*         exclusive scans (vector row pointers, scratch offsets) and a
 //                      histogram of replay classes.
 //   svc_emit_sorted    bitmap -> ascending column list by a popc prefix scan; value
 //                      vectors placed with prefix[word] + popc(lower bits).
@@ -27,8 +27,12 @@
 //                      fixed length is "first come, first served" along each key's
 //                      probe path, which has a unique fixed point: slot = the first
 //                      one on my path not held by an earlier element.  The team finds
-//                      it in parallel with atomicMin on the element's sequence number;
+//                      it in parallel with atomicMin on the element's sequence number (an
+//                      element pushed out of a slot by an earlier one starts its path again);
 //                      table growth steps are replayed level by level (8, 32, 128, ...).
+// The replay kernels take their groups from per-class lists (written by the scan kernel)
+// through a work counter, so a CTA never walks over groups of other classes and the
+// groups of a class, whose cost differs by an order of magnitude, balance themselves.
 #include "svc.cuh"
 
 #include <mutex>
@@ -53,14 +57,17 @@ constexpr int kClassM1 = 2;       // u <= 1228  (table <= 2048):  CTA team, ever
 constexpr int kClassM2 = 3;       // u <= 4914  (table <= 8192):  CTA team, everything in shared memory
 constexpr int kClassL = 4;        // table <= 32768:              CTA team, table in shared memory, lists in global
 constexpr int kClassXL = 5;       // larger:                      CTA team, table and lists in global
-constexpr int kNumClasses = 6;
+constexpr int kClassXS = 6;       // u <= 76    (table <= 128):   warp team, small enough for 48 resident teams per SM
+constexpr int kNumClasses = kSvcClasses;
+static_assert(kNumClasses == 7, "class numbering");
 
+constexpr int kXSCapU = 76, kXSCapT = 128;
 constexpr int kSCapU = 306, kSCapT = 512;
 constexpr int kM1CapU = 1228, kM1CapT = 2048;
 constexpr int kM2CapU = 4914, kM2CapT = 8192;
 constexpr int kLCapT = 32768;
-constexpr int kLStateInts = 19664;   // a table of kLCapT slots holds fewer than 19661 keys; STATE of class L sits in shared memory
-constexpr int kListsPerGroup = 5;   // X2, NEW, P, Q, STATE (the sixth list is the output slice)
+constexpr int kLSeqInts = 19664;    // a table of kLCapT slots holds fewer than 19661 keys; class L keeps the level's sequence in shared memory
+constexpr int kListsPerGroup = 4;   // X2, NEW, P, Q (the fifth list is the output slice)
 
 __host__ __device__ inline void next_level(int size, long long& trig, int& next_size) {
     const long long mask = size - 1;
@@ -85,6 +92,7 @@ __host__ __device__ inline int final_table_len(int distinct) {
 
 __host__ __device__ inline int replay_class(int u, int tbl_len) {
     if (tbl_len == 0) return kClassSorted;
+    if (u <= kXSCapU) return kClassXS;
     if (u <= kSCapU) return kClassS;
     if (u <= kM1CapU) return kClassM1;
     if (u <= kM2CapU) return kClassM2;
@@ -129,6 +137,7 @@ struct WarpTeam {
     __device__ static bool any(bool p, int*) { return __any_sync(0xffffffffu, p); }
     __device__ static int sum(int v, int*) { return warp_sum(v); }
     __device__ static int max_of(int v, int*) { return warp_max(v); }
+    __device__ static int broadcast(int v, int*) { return __shfl_sync(0xffffffffu, v, 0); }   // value of thread 0
     // rank of this thread among the flagged threads of the team, in thread order
     __device__ static int rank(bool flag, int& total, int*) {
         const unsigned b = __ballot_sync(0xffffffffu, flag);
@@ -162,6 +171,13 @@ struct BlockTeam {
         for (int w = 1; w < THREADS / 32; ++w) t = max(t, scratch[w]);
         __syncthreads();
         return t;
+    }
+    __device__ static int broadcast(int v, int* scratch) {     // value of thread 0
+        if (threadIdx.x == 0) scratch[32] = v;
+        __syncthreads();
+        const int r = scratch[32];
+        __syncthreads();
+        return r;
     }
     // exclusive prefix sum of v over the threads of the block, in thread order
     __device__ static int scan_exclusive(int v, int& total, int* scratch) {
@@ -252,64 +268,152 @@ svc_count_kernel(SvcProblem p, int words, int filter, int* __restrict__ counts, 
     }
 }
 
-// ---------------------------------------------------------------- scans (one CTA)
-// totals: [0] nvec, [1] scratch ints, [2..2+kNumClasses) groups per replay class
-__global__ void __launch_bounds__(1024)
-svc_scan_kernel(int m_vec, int* __restrict__ vec_ptr, const int* __restrict__ tbl_len, long long* __restrict__ tbl_off,
-                long long* __restrict__ totals) {
-    __shared__ long long sh_a[32], sh_b[32];
-    __shared__ long long carry_a, carry_b;
-    __shared__ int hist[kNumClasses];
+// ---------------------------------------------------------------- scans
+// Exclusive scans over the groups (vector row pointers from the counts, scratch offsets) and the lists of replayed
+// groups per class, in three small launches: per-block sums, a scan of the block sums by one CTA, and the final
+// positions.  A block covers kScanBlock groups; a block sum is kScanFields numbers: vectors, scratch ints, and
+// the groups of each replay class.
+// totals: [0] nvec, [1] scratch ints, [2..2+kNumClasses) groups per replay class, then the bad-column flag
+constexpr int kScanThreads = 1024;
+constexpr int kScanPerThread = 4;
+constexpr int kScanBlock = kScanThreads * kScanPerThread;
+constexpr int kScanFields = 2 + kNumClasses;
+
+// Sums `v` over the block; the result is valid in every thread.  sh: 32 long longs.
+__device__ __forceinline__ long long block_sum_ll(long long v, long long* sh) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    if (threadIdx.x == 0) { carry_a = 0; carry_b = 0; }
-    if (threadIdx.x < kNumClasses) hist[threadIdx.x] = 0;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if (lane == 0) sh[warp] = v;
     __syncthreads();
-    for (int base = 0; base < m_vec; base += 1024) {
-        const int i = base + threadIdx.x;
-        long long a = 0, b = 0;
-        if (i < m_vec) {
-            a = vec_ptr[i];
-            b = group_scratch_ints((int)a, tbl_len[i]);
-            atomicAdd(&hist[replay_class((int)a, tbl_len[i])], 1);
-        }
-        long long ia = a, ib = b;
+    long long t = 0;
+    for (int w = 0; w < kScanThreads / 32; ++w) t += sh[w];
+    __syncthreads();
+    return t;
+}
+// Exclusive prefix of `v` over the threads of the block, in thread order.  sh: 32 long longs.
+__device__ __forceinline__ long long block_prefix_ll(long long v, long long* sh) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    long long inc = v;
 #pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const long long ta = __shfl_up_sync(0xffffffffu, ia, o);
-            const long long tb = __shfl_up_sync(0xffffffffu, ib, o);
-            if (lane >= o) { ia += ta; ib += tb; }
-        }
-        if (lane == 31) { sh_a[warp] = ia; sh_b[warp] = ib; }
-        __syncthreads();
-        if (warp == 0) {
-            long long wa = sh_a[lane], wb = sh_b[lane];
+    for (int o = 1; o < 32; o <<= 1) {
+        const long long t = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += t;
+    }
+    if (lane == 31) sh[warp] = inc;
+    __syncthreads();
+    long long before = 0;
+    for (int w = 0; w < warp; ++w) before += sh[w];
+    __syncthreads();
+    return before + inc - v;
+}
+
+__global__ void __launch_bounds__(kScanThreads)
+svc_scan_sums_kernel(int m_vec, const int* __restrict__ counts, const int* __restrict__ tbl_len,
+                     long long* __restrict__ block_sums) {
+    __shared__ long long sh[32];
+    long long f[kScanFields];
 #pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const long long ta = __shfl_up_sync(0xffffffffu, wa, o);
-                const long long tb = __shfl_up_sync(0xffffffffu, wb, o);
-                if (lane >= o) { wa += ta; wb += tb; }
-            }
-            sh_a[lane] = wa; sh_b[lane] = wb;
+    for (int k = 0; k < kScanFields; ++k) f[k] = 0;
+    const int first = blockIdx.x * kScanBlock + threadIdx.x * kScanPerThread;
+#pragma unroll
+    for (int j = 0; j < kScanPerThread; ++j) {
+        const int i = first + j;
+        if (i >= m_vec) break;
+        const int u = counts[i], len = tbl_len[i];
+        f[0] += u;
+        f[1] += group_scratch_ints(u, len);
+        const int c = replay_class(u, len);
+#pragma unroll
+        for (int k = 0; k < kNumClasses; ++k) f[2 + k] += (c == k) ? 1 : 0;
+    }
+#pragma unroll
+    for (int k = 0; k < kScanFields; ++k) {
+        const long long t = block_sum_ll(f[k], sh);
+        if (threadIdx.x == 0) block_sums[(size_t)blockIdx.x * kScanFields + k] = t;
+    }
+}
+
+// One CTA: block_sums -> exclusive prefixes in place, and the totals.
+__global__ void __launch_bounds__(kScanThreads)
+svc_scan_blocks_kernel(int n_blocks, long long* __restrict__ block_sums, long long* __restrict__ totals) {
+    __shared__ long long sh[32];
+    __shared__ long long carry[kScanFields];
+    if (threadIdx.x < kScanFields) carry[threadIdx.x] = 0;
+    __syncthreads();
+    for (int b0 = 0; b0 < n_blocks; b0 += kScanThreads) {
+        const int b = b0 + threadIdx.x;
+        for (int k = 0; k < kScanFields; ++k) {
+            const long long v = (b < n_blocks) ? block_sums[(size_t)b * kScanFields + k] : 0;
+            const long long ex = block_prefix_ll(v, sh);
+            const long long c0 = carry[k];
+            if (b < n_blocks) block_sums[(size_t)b * kScanFields + k] = c0 + ex;
+            __syncthreads();
+            if (threadIdx.x == kScanThreads - 1) carry[k] = c0 + ex + v;
+            __syncthreads();
         }
-        __syncthreads();
-        const long long off_a = carry_a + (warp ? sh_a[warp - 1] : 0);
-        const long long off_b = carry_b + (warp ? sh_b[warp - 1] : 0);
-        if (i < m_vec) {
-            vec_ptr[i] = (int)(off_a + ia - a);
-            tbl_off[i] = off_b + ib - b;
-        }
-        __syncthreads();
-        if (threadIdx.x == 1023) { carry_a = off_a + ia; carry_b = off_b + ib; }
-        __syncthreads();
     }
     if (threadIdx.x == 0) {
-        vec_ptr[m_vec] = (int)carry_a;
-        tbl_off[m_vec] = carry_b;
-        totals[0] = carry_a;
-        totals[1] = carry_b;
-        for (int c = 0; c < kNumClasses; ++c) totals[2 + c] = hist[c];
-        totals[2 + kNumClasses] = g_svc_bad_column;      // reported with the totals, then cleared
+        for (int k = 0; k < kScanFields; ++k) totals[k] = carry[k];
+        totals[kScanFields] = g_svc_bad_column;          // reported with the totals, then cleared
         g_svc_bad_column = 0;
+    }
+}
+
+// vec_ptr: counts in, exclusive scan out (and the total at [m_vec]); tbl_off: scratch offsets; class_list: the
+// replayed groups class by class (S first), inside a class in ascending order.
+__global__ void __launch_bounds__(kScanThreads)
+svc_scan_place_kernel(int m_vec, int* __restrict__ vec_ptr, const int* __restrict__ tbl_len,
+                      long long* __restrict__ tbl_off, const long long* __restrict__ block_sums,
+                      const long long* __restrict__ totals, int* __restrict__ class_list) {
+    __shared__ long long sh[32];
+    const int first = blockIdx.x * kScanBlock + threadIdx.x * kScanPerThread;
+    int u[kScanPerThread], cls[kScanPerThread];
+    long long scr[kScanPerThread];
+    long long f[kScanFields];
+#pragma unroll
+    for (int k = 0; k < kScanFields; ++k) f[k] = 0;
+#pragma unroll
+    for (int j = 0; j < kScanPerThread; ++j) {
+        const int i = first + j;
+        u[j] = 0; scr[j] = 0; cls[j] = -1;
+        if (i < m_vec) {
+            u[j] = vec_ptr[i];
+            const int len = tbl_len[i];
+            scr[j] = group_scratch_ints(u[j], len);
+            cls[j] = replay_class(u[j], len);
+            f[0] += u[j];
+            f[1] += scr[j];
+#pragma unroll
+            for (int k = 0; k < kNumClasses; ++k) f[2 + k] += (cls[j] == k) ? 1 : 0;
+        }
+    }
+    // where class c starts in the list: after all groups of the classes before it (class 0 is not replayed)
+    long long at[kScanFields];
+#pragma unroll
+    for (int k = 0; k < kScanFields; ++k)
+        at[k] = block_sums[(size_t)blockIdx.x * kScanFields + k] + block_prefix_ll(f[k], sh);
+    long long class_base = 0;
+#pragma unroll
+    for (int k = 1; k < kNumClasses; ++k) {
+        at[2 + k] += class_base;
+        class_base += totals[2 + k];
+    }
+#pragma unroll
+    for (int j = 0; j < kScanPerThread; ++j) {
+        const int i = first + j;
+        if (i >= m_vec) break;
+        vec_ptr[i] = (int)at[0];
+        tbl_off[i] = at[1];
+        at[0] += u[j];
+        at[1] += scr[j];
+#pragma unroll
+        for (int k = 1; k < kNumClasses; ++k)
+            if (cls[j] == k) class_list[at[2 + k]++] = i;
+    }
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        vec_ptr[m_vec] = (int)totals[0];
+        tbl_off[m_vec] = totals[1];
     }
 }
 
@@ -433,15 +537,11 @@ __device__ __forceinline__ int find_slot(const int* tab, unsigned mask, int key)
     return (int)(p.i + p.w);
 }
 
-// STATE word of one element during a level: bits 0..23 window start, 24..27 offset, 28..30 jumps, 31 settled.
-// perturb is recomputed as key >> (5 * jumps); jumps saturates at 7 (perturb is 0 from the 7th jump on for keys < 2^31).
-__device__ __forceinline__ unsigned pack_state(const Probe& p, unsigned jumps, bool settled) {
-    return (p.i & 0xffffffu) | (p.w << 24) | (min(jumps, 7u) << 28) | (settled ? 0x80000000u : 0u);
-}
-
 struct ReplayBuffers {
-    int* table;     // cap ints
-    int* lists[6];  // six lists of u ints: two of them alternate as the ordered list (one is the output slice)
+    int* table;      // cap ints
+    int* lists[4];   // lists of u ints: X2 (alternates with the output slice as the ordered list), NEW, P, Q
+    int* seq_local;  // non-null: u ints of shared memory that hold the insertion sequence of the current level
+                     // (the lists are then in global memory and are only streamed through)
 };
 
 // Ordered extraction: keys of `tab` in slot order into dst; returns how many.  With seq != null the
@@ -572,9 +672,10 @@ __device__ void replay_group(const SvcProblem& p, int i, int u_final, int cap, i
     int* x = (n_rebuilds & 1) ? bufs.lists[0] : out_slice;      // list before the first rebuild (empty)
     int* xn = (n_rebuilds & 1) ? out_slice : bufs.lists[0];     // written by the first rebuild
     int* const fresh = bufs.lists[1];                           // NEW: columns of the row not yet in the set
-    int* seq = bufs.lists[2];                                   // insertion sequence of the current level
-    int* seq_other = bufs.lists[3];
-    unsigned* const state = reinterpret_cast<unsigned*>(bufs.lists[4]);
+    // insertion sequence of the current level, and the list the next level's head is extracted into: two lists
+    // that swap roles, or (seq_local) a fixed shared-memory sequence refilled from one extraction list
+    int* seq = bufs.seq_local ? bufs.seq_local : bufs.lists[2];
+    int* ext = bufs.seq_local ? bufs.lists[2] : bufs.lists[3];
 
     int n_cur = 0;
     unsigned mask_prev = kMinTable - 1;
@@ -611,7 +712,15 @@ __device__ void replay_group(const SvcProblem& p, int i, int u_final, int cap, i
             const int trig = (int)(trig_ll > 0x7fffffff ? 0x7fffffff : trig_ll);
             const int n_l = min(trig, n_total);
             mask = (unsigned)size - 1u;
-            for (int s = tid; s < size; s += Team::kSize) tab[s] = kEmptyPrio;
+            if (size >= 4 * Team::kSize) {
+                const int4 fill = make_int4(kEmptyPrio, kEmptyPrio, kEmptyPrio, kEmptyPrio);
+                int4* t4 = reinterpret_cast<int4*>(tab);
+                for (int s = tid; s < size / 4; s += Team::kSize) t4[s] = fill;
+            } else {
+                for (int s = tid; s < size; s += Team::kSize) tab[s] = kEmptyPrio;
+            }
+            if (bufs.seq_local)                                                  // head of the sequence: last level's table order
+                for (int q = tid; q < e_len; q += Team::kSize) seq[q] = ext[q];
             for (int q = e_len + tid; q < n_l; q += 4 * Team::kSize) {          // four loads in flight
                 int v4[4];
 #pragma unroll
@@ -626,7 +735,7 @@ __device__ void replay_group(const SvcProblem& p, int i, int u_final, int cap, i
             Team::sync();
             const int first_new = max(e_len, n_cur);
             bool dup_here = false;          // also raised when a bound is hit: the group is then redone sequentially
-            volatile unsigned* vstate = state;
+            volatile int* vtab = tab;
             for (int q4 = tid; q4 < n_l && !dup_here; q4 += 4 * Team::kSize) {
               int k4[4];
 #pragma unroll
@@ -635,27 +744,29 @@ __device__ void replay_group(const SvcProblem& p, int i, int u_final, int cap, i
               for (int b = 0; b < 4; ++b) {
                 const int q = q4 + b * Team::kSize;
                 if (q >= n_l || dup_here) break;
-                int e = q;
-                Probe pr = probe_begin(k4[b], mask);
-                unsigned jumps = 0;
+                int e = q, key = k4[b];
+                Probe pr = probe_begin(key, mask);
                 for (unsigned tries = 0;; ++tries) {
-                    vstate[e] = pack_state(pr, jumps, true);     // where e sits if the next claim succeeds
-                    __threadfence_block();
-                    const int old = atomicMin(&tab[pr.i + pr.w], e);
-                    if (old > e) {
-                        if (old == kEmptyPrio) break;            // free slot taken: this chain ends
-                        // a later element sat here: carry it on from the position it recorded
-                        __threadfence_block();
-                        e = old;
-                        const unsigned st = vstate[e];
-                        jumps = (st >> 28) & 7u;
-                        pr.i = st & 0xffffffu; pr.w = (st >> 24) & 15u;
-                        pr.perturb = (jumps >= 7u) ? 0u : ((unsigned)seq[e] >> (kPerturbShift * jumps));
-                    } else if ((e >= first_new && seq[old] == seq[e]) || tries > 16u * mask + 256u) {
+                    const int slot = (int)(pr.i + pr.w);
+                    // Slot values only ever decrease during a level, so a slot seen with an earlier element stays
+                    // out of reach; only a slot that looks free or later is worth the atomic.
+                    int cur = vtab[slot];
+                    if (cur > e) cur = atomicMin(&tab[slot], e);
+                    if (cur > e) {
+                        if (cur == kEmptyPrio) break;            // free slot taken: this chain ends
+                        // a later element sat here: the same thread carries it on, from the start of its own path
+                        // (every slot it passed before still holds an earlier element, so it walks to the same
+                        // place and beyond)
+                        e = cur;
+                        key = seq[e];
+                        pr = probe_begin(key, mask);
+                        continue;
+                    }
+                    if ((e >= first_new && seq[cur] == key) || tries > 16u * mask + 256u) {
                         dup_here = true;
                         break;
                     }
-                    if (probe_advance(pr, mask)) ++jumps;
+                    probe_advance(pr, mask);
                 }
               }
             }
@@ -666,8 +777,8 @@ __device__ void replay_group(const SvcProblem& p, int i, int u_final, int cap, i
                 n_cur = extract_ordered<Team>(tab, size, seq, xn, red);
                 break;
             }
-            e_len = extract_ordered<Team>(tab, size, seq, seq_other, red);
-            int* t3 = seq; seq = seq_other; seq_other = t3;
+            e_len = extract_ordered<Team>(tab, size, seq, ext, red);
+            if (!bufs.seq_local) { int* t3 = seq; seq = ext; ext = t3; }
             size = (next_size > cap) ? cap : next_size;
         }
         if (duplicate) break;
@@ -688,6 +799,8 @@ __device__ void replay_group(const SvcProblem& p, int i, int u_final, int cap, i
     // here: out_slice holds the ordered list, tab holds its keys at their slots
     if (out_vals && n_cur > 0) {
         const int size = (int)mask_prev + 1;
+        // a list that is free by now (the group is finished with its sequences)
+        unsigned* const state = reinterpret_cast<unsigned*>(bufs.seq_local ? bufs.seq_local : bufs.lists[1]);
         int n = 0;
         for (int s0 = 0; s0 < size; s0 += Team::kSize) {        // slot -> position
             const int s = s0 + tid;
@@ -719,28 +832,35 @@ __device__ void replay_group(const SvcProblem& p, int i, int u_final, int cap, i
 }
 
 template <class Team, int CLASS>
-__global__ void __launch_bounds__(Team::kSize * Team::kPerBlock, 1)
+__global__ void __launch_bounds__(Team::kSize * Team::kPerBlock,
+                                  ((CLASS == kClassM1 || CLASS == kClassXS) ? 1536 : 1024) / (Team::kSize * Team::kPerBlock))
 svc_emit_replay_kernel(SvcProblem p, const int* __restrict__ vec_ptr, const int* __restrict__ tbl_len,
                        const long long* __restrict__ tbl_off, int* __restrict__ scratch, int* __restrict__ out_col,
-                       __half* __restrict__ out_vals, int smem_table_ints, int smem_list_ints) {
+                       __half* __restrict__ out_vals, int smem_table_ints, int smem_list_ints,
+                       const int* __restrict__ groups, int n_groups, int* __restrict__ queue) {
     extern __shared__ int sm_ints[];
-    __shared__ int red[33];
+    __shared__ int red[34];
     const int per_team = smem_table_ints + kListsPerGroup * smem_list_ints;
     int* mine = sm_ints + (size_t)Team::index_in_block() * per_team;
-    for (int i = blockIdx.x * Team::kPerBlock + Team::index_in_block(); i < p.m_vec; i += gridDim.x * Team::kPerBlock) {
+    for (;;) {
+        int k = 0;
+        if (Team::tid() == 0) k = atomicAdd(queue, 1);
+        k = Team::broadcast(k, red);
+        if (k >= n_groups) break;
+        const int i = groups[k];
         const int base = vec_ptr[i];
         const int u = vec_ptr[i + 1] - base;
         const int cap = tbl_len[i];
-        if (replay_class(u, cap) != CLASS) continue;
         ReplayBuffers b;
-        if (CLASS == kClassS || CLASS == kClassM1 || CLASS == kClassM2) {
+        b.seq_local = nullptr;
+        if (CLASS == kClassXS || CLASS == kClassS || CLASS == kClassM1 || CLASS == kClassM2) {
             b.table = mine;
             for (int l = 0; l < kListsPerGroup; ++l) b.lists[l] = mine + smem_table_ints + l * smem_list_ints;
         } else {
             int* g = scratch + tbl_off[i];
             for (int l = 0; l < kListsPerGroup; ++l) b.lists[l] = g + (size_t)l * u;
             b.table = (CLASS == kClassL) ? mine : g + (size_t)kListsPerGroup * u;
-            if (CLASS == kClassL) b.lists[4] = mine + smem_table_ints;       // STATE: written and read per insertion step
+            if (CLASS == kClassL) b.seq_local = mine + smem_table_ints;
         }
         replay_group<Team>(p, i, u, cap, base, b, out_col, out_vals, red);
     }
@@ -749,7 +869,7 @@ svc_emit_replay_kernel(SvcProblem p, const int* __restrict__ vec_ptr, const int*
 int device_sm_count() { return current_device_sm_count(); }
 
 // Side streams so that launches working on disjoint groups overlap (fork from / join into the caller's stream).
-constexpr int kAuxStreams = 5;
+constexpr int kAuxStreams = 6;
 struct Aux {
     cudaStream_t stream[kAuxStreams];
     cudaEvent_t fork, join[kAuxStreams];
@@ -800,11 +920,11 @@ struct Fork {
 
 template <class Team, int CLASS>
 cudaError_t launch_replay(const SvcProblem& p, const SvcScratch& s, int* out_col, __half* out_vals, long long groups,
-                          int table_ints, int list_ints, cudaStream_t stream) {
+                          long long first, int table_ints, int list_ints, cudaStream_t stream) {
     if (groups <= 0) return cudaSuccess;
     auto kern = svc_emit_replay_kernel<Team, CLASS>;
     const size_t smem = ((size_t)Team::kPerBlock * (table_ints + (size_t)kListsPerGroup * list_ints) +
-                         (CLASS == kClassL ? kLStateInts : 0)) * sizeof(int);
+                         (CLASS == kClassL ? kLSeqInts : 0)) * sizeof(int);
     static DeviceOnce once;
     if (!once.done()) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -816,12 +936,13 @@ cudaError_t launch_replay(const SvcProblem& p, const SvcScratch& s, int* out_col
     }
     const int sms = device_sm_count();
     long long want = (groups + Team::kPerBlock - 1) / Team::kPerBlock;
-    // every block scans all groups for its class: a few blocks per SM are enough
-    const long long cap_blocks = (long long)sms * (smem > 100 * 1024 ? 1 : (smem > 40 * 1024 ? 3 : 6));
+    // as many blocks as can be resident: the groups are handed out through the class's work counter
+    const long long cap_blocks = (long long)sms * (smem > 113 * 1024 ? 1 : (smem > 75 * 1024 ? 2 : (smem > 56 * 1024 ? 3 : (smem > 45 * 1024 ? 4 : (smem > 28 * 1024 ? 6 : 8)))));
     int grid = (int)(want < cap_blocks ? want : cap_blocks);
     if (grid < 1) grid = 1;
     kern<<<grid, Team::kSize * Team::kPerBlock, smem, stream>>>(p, s.vec_ptr, s.tbl_len, s.tbl_off, s.tables, out_col,
-                                                                 out_vals, table_ints, list_ints);
+                                                                 out_vals, table_ints, list_ints, s.class_list + first,
+                                                                 (int)groups, s.queue + CLASS);
     return cudaGetLastError();
 }
 
@@ -863,7 +984,11 @@ cudaError_t svc_count_and_scan(const SvcProblem& p, const SvcScratch& s, bool /*
         }
         if (e != cudaSuccess) return e;
     }
-    svc_scan_kernel<<<1, 1024, 0, stream>>>(p.m_vec, s.vec_ptr, s.tbl_len, s.tbl_off, s.totals);
+    const int n_blocks = p.m_vec > 0 ? (p.m_vec + kScanBlock - 1) / kScanBlock : 1;
+    svc_scan_sums_kernel<<<n_blocks, kScanThreads, 0, stream>>>(p.m_vec, s.vec_ptr, s.tbl_len, s.block_sums);
+    svc_scan_blocks_kernel<<<1, kScanThreads, 0, stream>>>(n_blocks, s.block_sums, s.totals);
+    svc_scan_place_kernel<<<n_blocks, kScanThreads, 0, stream>>>(p.m_vec, s.vec_ptr, s.tbl_len, s.tbl_off, s.block_sums, s.totals,
+                                                                 s.class_list);
     return cudaGetLastError();
 }
 
@@ -877,6 +1002,9 @@ cudaError_t svc_emit(const SvcProblem& p, const SvcScratch& s, const long long* 
     if (e == cudaSuccess) e = allow_big_smem(svc_emit_sorted_kernel<WarpTeam>, once_warp, 208 * 1024);
     if (e != cudaSuccess) return e;
 
+    // the work counters of the replay classes, cleared before the side streams fork off
+    e = cudaMemsetAsync(s.queue, 0, 8 * sizeof(int), stream);
+    if (e != cudaSuccess) return e;
     std::lock_guard<std::mutex> lk(g_aux_mu);
     Fork f(aux_for_device(), stream);
     if (class_groups[kClassSorted] > 0) {
@@ -893,16 +1021,21 @@ cudaError_t svc_emit(const SvcProblem& p, const SvcScratch& s, const long long* 
         e = cudaGetLastError();
         if (e != cudaSuccess) return e;
     }
+    // where each class starts in the list of replayed groups (the order svc_scan_place_kernel writes them in)
+    long long first[kNumClasses] = {0};
+    for (int c = 2; c < kNumClasses; ++c) first[c] = first[c - 1] + class_groups[c - 1];
     // the largest groups first: they are the critical path
-    e = launch_replay<BlockTeam<1024>, kClassXL>(p, s, out_col, out_vals, class_groups[kClassXL], 0, 0, f.next());
+    e = launch_replay<BlockTeam<1024>, kClassXL>(p, s, out_col, out_vals, class_groups[kClassXL], first[kClassXL], 0, 0, f.next());
     if (e == cudaSuccess)
-        e = launch_replay<BlockTeam<1024>, kClassL>(p, s, out_col, out_vals, class_groups[kClassL], kLCapT, 0, f.next());
+        e = launch_replay<BlockTeam<1024>, kClassL>(p, s, out_col, out_vals, class_groups[kClassL], first[kClassL], kLCapT, 0, f.next());
     if (e == cudaSuccess)
-        e = launch_replay<BlockTeam<512>, kClassM2>(p, s, out_col, out_vals, class_groups[kClassM2], kM2CapT, kM2CapU + 2, f.next());
+        e = launch_replay<BlockTeam<512>, kClassM2>(p, s, out_col, out_vals, class_groups[kClassM2], first[kClassM2], kM2CapT, kM2CapU + 2, f.next());
     if (e == cudaSuccess)
-        e = launch_replay<BlockTeam<256>, kClassM1>(p, s, out_col, out_vals, class_groups[kClassM1], kM1CapT, kM1CapU + 4, f.next());
+        e = launch_replay<BlockTeam<256>, kClassM1>(p, s, out_col, out_vals, class_groups[kClassM1], first[kClassM1], kM1CapT, kM1CapU + 4, f.next());
     if (e == cudaSuccess)
-        e = launch_replay<WarpTeam, kClassS>(p, s, out_col, out_vals, class_groups[kClassS], kSCapT, kSCapU + 2, stream);
+        e = launch_replay<WarpTeam, kClassS>(p, s, out_col, out_vals, class_groups[kClassS], first[kClassS], kSCapT, kSCapU + 2, f.next());
+    if (e == cudaSuccess)
+        e = launch_replay<WarpTeam, kClassXS>(p, s, out_col, out_vals, class_groups[kClassXS], first[kClassXS], kXSCapT, kXSCapU + 2, stream);
     if (e != cudaSuccess) return e;
     return f.join();
 }
