@@ -138,11 +138,12 @@ def test_power_law_sweep_sample(lib):
     assert_close(gpu_spmm(ptr, col, vals, rhs, 8, torch.float32, kernel=ops.KERNEL_GATHER_LSU), ref, fp32=True)
 
 
-def test_long_rows_are_split_and_summed(lib):
-    """A few vector rows far longer than the rest (split into chunks whose partial tiles are summed),
-    next to empty and short rows; N with a partial column tile."""
-    rng = np.random.default_rng(21)
-    K, V, N = 20000, 8, 200
+@pytest.mark.parametrize("V,N", [(8, 200), (16, 256), (16, 72)])
+def test_long_rows_are_split_and_summed(lib, V, N):
+    """A few vector rows far longer than the rest (split into chunks; the chunk that finishes last adds the partial
+    tiles up inside the kernel), next to empty and short rows; N with and without a partial column tile."""
+    rng = np.random.default_rng(21 + V + N)
+    K = 20000
     lens = [15000, 3, 0, 9000] + [int(x) for x in rng.integers(0, 40, 400)] + [12000]
     ptr, col, vals = random_cvse(rng, len(lens), K, V, lens)
     rhs = rng.normal(0, 1, (K, N)).astype(np.float16)
@@ -150,6 +151,35 @@ def test_long_rows_are_split_and_summed(lib):
     for dt in (torch.float32, torch.float16):
         got = gpu_spmm(ptr, col, vals, rhs, V, dt, kernel=ops.KERNEL_GATHER_LSU)
         assert_close(got, ref, fp32=dt == torch.float32)
+
+
+def test_row_gather_workspace_is_reusable_and_optional(lib):
+    """The caller-owned workspace of the row-gather kernel holds its work counter, the list of split rows and their
+    arrival counters: the same buffer serves call after call (dirty from the last one), and without any workspace
+    the kernel deals its rows out round robin and splits nothing -- same numbers every time."""
+    rng = np.random.default_rng(5)
+    K, V, N = 12000, 8, 128
+    lens = [7000, 0, 2500] + [int(x) for x in rng.integers(0, 90, 900)]
+    ptr, col, vals = random_cvse(rng, len(lens), K, V, lens)
+    rhs = rng.normal(0, 1, (K, N)).astype(np.float16)
+    ref = spmm_oracle.sspmm_host(V, ptr, col, vals, rhs, threads=8)
+    d = lambda t: torch.from_numpy(t).to(DEV)
+    vp, vc, vv, B = d(ptr), d(col), d(vals), d(rhs)
+    need = ops.workspace_bytes(len(lens), V, N, K, int(ptr[-1]))
+    assert need > 256                      # long rows: the workspace holds more than the counter
+    ws = torch.full((need,), 0xAB, dtype=torch.uint8, device=DEV)
+    ops.set_kernel(ops.KERNEL_GATHER_LSU)
+    try:
+        for _ in range(3):
+            got = ops.sspmm_ws(vp, vc, vv, B, V, int(ptr[-1]), ws)
+            torch.cuda.synchronize()
+            assert_close(got.float().cpu().numpy(), ref)
+        got = ops.sspmm_ws(vp, vc, vv, B, V, int(ptr[-1]), None)
+        torch.cuda.synchronize()
+        assert_close(got.float().cpu().numpy(), ref)
+    finally:
+        ops.set_kernel(ops.KERNEL_AUTO)
+    assert ops.device_status() == 0
 
 
 def test_conv_layer_full_width_properties(lib):
