@@ -290,8 +290,7 @@ def run_ours(args):
     useful_flops_total = sum(2.0 * p["nnz"] * N_total for p in probs)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
 
-    # ---- one step = every product once = ONE group run (a grouped expansion launch + one persistent
-    # tensor-core launch, or that launch alone, see sspmm_group_create)
+    # ---- one step = every product once = ONE group run = one persistent tensor-core launch (see sspmm_group_create)
     if not all(p["plan"].one_launch for p in probs):
         raise RuntimeError("a conv operand did not qualify for the grouped kernel")
     group = ops.Group([(p["plan"], p["vv"], p["B"], p["C"]) for p in probs], mode=args.group_mode)
@@ -366,7 +365,7 @@ def run_ours(args):
         roof = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                 "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"] + " copy"}
     sus_tf = f_alg.sum() / (sustained_ms * 1e-3) / 1e12
-    roof.update({"traffic": None, "kernel": "sspmm_fused_kernel" + (" (+ expand_group_kernel)" if launches_per_step == 2 else ""),
+    roof.update({"traffic": None, "kernel": "sspmm_fused_pair_kernel" if args.group_mode == 3 else "sspmm_fused_kernel",
                  "t_hbm_over_t": float(t_hbm / step_s), "t_tensor_over_t": float(t_tensor / step_s),
                  "algorithmic_flops_per_step": float(f_alg.sum()), "algorithmic_bytes_per_step": float(b_alg.sum()),
                  "hbm_gbs_algorithmic": float(b_alg.sum() / step_s / 1e9),
@@ -585,7 +584,7 @@ def run_ours(args):
                 "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
                 "config": {"workload": WORKLOAD if not args.only else "single product " + args.only, "N_total": N_total,
                            "N_per_gpu": n_loc, "products_per_step": len(probs), "cuda_graph": graphed,
-                           "group": {"mode": ("automatic", "compressed", "expanded")[args.group_mode], "launches_per_step": launches_per_step,
+                           "group": {"mode": ("automatic", "compressed", "expanded", "expanded, CTA pairs")[args.group_mode], "launches_per_step": launches_per_step,
                                      "tile_columns": group.tile_columns, "work_items": group.work_items, "ctas": group.ctas,
                                      "scratch_bytes": group.scratch_bytes},
                            "l2": "operands of a step exceed L2 and a 256 MiB buffer is written between steps",
@@ -939,6 +938,9 @@ def run_case(name: str):
          group_conv_layer   conv layer (512, 4608) s = 0.8 V = 16, N = 18944, as a group, expanded and compressed
          planned_conv_layer the same layer through sspmm_planned (one launch, A tiles built in the kernel), N = 9472
          sweep_stack        32 sweep matrices: stacked SVC (svc_batch), then the SpMM of each at N = 128
+         svc_stack8         stacked SVC of sweep matrices 0..7, twice (small enough for a full counter capture)
+         svc_stack125       stacked SVC of sweep matrices 0..124, twice (one stack of the 2000-matrix sweep)
+         gather_sweep       row-gather SpMM of sweep matrix 7 (n = 51970) at N = 128, four times
          svc_powerlaw       SVC of one power-law matrix, n = 65536, V = 8, three times
          gather_powerlaw    row-gather SpMM of that matrix at N = 1024, four times"""
     import torch
@@ -981,6 +983,17 @@ def run_case(name: str):
             for (n, p, c, v), (vp, vc, vv) in zip(mats, parts):
                 B = torch.randn((n, 128), device=dev, dtype=torch.float16)
                 ops.sspmm_ws(vp, vc, vv, B, 8, vc.numel(), ws)
+    elif name in ("svc_stack8", "svc_stack125"):
+        mats = [synthetic.sweep_matrix_device(i, dev) for i in range(8 if name == "svc_stack8" else 125)]
+        for _ in range(2):
+            ops.svc_batch([(p, c, v, n, n) for n, p, c, v in mats], 8)
+    elif name == "gather_sweep":
+        n, p, c, v = synthetic.sweep_matrix_device(7, dev)
+        vp, vc, vv, _ = ops.svc(p, c, v, n, n, 8)
+        B = torch.randn((n, 128), device=dev, dtype=torch.float16)
+        ws = torch.empty(max(ops.workspace_bytes(vp.numel() - 1, 8, 128, n, vc.numel()), 256), dtype=torch.uint8, device=dev)
+        for _ in range(4):
+            ops.sspmm_ws(vp, vc, vv, B, 8, vc.numel(), ws)
     elif name in ("svc_powerlaw", "gather_powerlaw"):
         p, c, v = synthetic.power_law_device(65536, 65536, dev)
         for _ in range(3):
@@ -1005,8 +1018,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--group-mode", type=int, default=0, choices=[0, 1, 2],
-                    help="0 automatic, 1 A tiles built in the kernel from the compressed operand, 2 dense copies of A written every step")
+    ap.add_argument("--group-mode", type=int, default=0, choices=[0, 1, 2, 3],
+                    help="0 automatic, 1 A tiles built in the kernel from the compressed operand, 2 dense copies of A written by "
+                         "the kernel's loader warps every step, 3 as 2 with 256 x 256 tiles on CTA pairs")
     ap.add_argument("--sweep-matrices", type=int, default=2000, help="matrices of the power-law sweep (whole job)")
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of a CUDA graph of the step")
     ap.add_argument("--no-extras", action="store_true", help="skip the SVC and FFN side measurements")

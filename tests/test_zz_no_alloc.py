@@ -82,6 +82,29 @@ def test_noalloc_matches_regular_entry_point_on_two_calls_in_a_row(lib):
         assert call_noalloc(lib, t[0], t[1], t[2], t[3], V, out) == 0
         torch.cuda.synchronize()
         assert_same(out, ref)
+    # "allocates nothing": after these warm calls, further calls leave the device's free memory and the default
+    # stream-ordered pool (the allocator the regular entry points use) exactly as they were
+    from cuda.bindings import runtime as cudart
+    err, pool = cudart.cudaDeviceGetDefaultMemPool(0)
+    assert err == cudart.cudaError_t.cudaSuccess
+
+    def pool_state():
+        vals = []
+        for attr in (cudart.cudaMemPoolAttr.cudaMemPoolAttrReservedMemCurrent, cudart.cudaMemPoolAttr.cudaMemPoolAttrUsedMemCurrent):
+            e, v = cudart.cudaMemPoolGetAttribute(pool, attr)
+            assert e == cudart.cudaError_t.cudaSuccess
+            vals.append(int(v))
+        return vals
+
+    outs = [torch.full_like(ref, float("nan")) for (_, _, ref) in prepared]
+    torch.cuda.synchronize()
+    before_pool, before_free = pool_state(), torch.cuda.mem_get_info()[0]
+    for _ in range(3):
+        for out, (t, V, ref) in zip(outs, prepared):
+            assert call_noalloc(lib, t[0], t[1], t[2], t[3], V, out) == 0
+    torch.cuda.synchronize()
+    assert pool_state() == before_pool
+    assert torch.cuda.mem_get_info()[0] == before_free
 
 
 def test_noalloc_rejects_what_does_not_fit(lib):
