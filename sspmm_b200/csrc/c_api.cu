@@ -252,7 +252,7 @@ struct svc_job {
     bool with_values;
     long long nvec;
     long long table_ints;
-    long long class_groups[kSvcClasses];
+    long long class_groups[kSvcSegs];      // groups per list segment; [0] = groups whose ascending order is exact
     int device;
     cudaStream_t stream;
 };
@@ -413,7 +413,7 @@ int svc_begin(int M, int K, int vec_length, const int* d_csr_row_ptr, const int*
     long long totals[kSvcTotals] = {0};
     if (e == cudaSuccess) e = cudaMemcpyAsync(totals, j->s.totals, sizeof totals, cudaMemcpyDeviceToHost, st);
     if (e == cudaSuccess) e = cudaStreamSynchronize(st);
-    const int bad = (int)totals[2 + kSvcClasses];
+    const int bad = (int)totals[2 + kSvcSegs];
     if (e != cudaSuccess || bad || totals[0] > 0x7fffffffLL) {
         cudaFreeAsync(base, st);
         delete j;
@@ -424,7 +424,7 @@ int svc_begin(int M, int K, int vec_length, const int* d_csr_row_ptr, const int*
     }
     j->nvec = totals[0];
     j->table_ints = totals[1];
-    for (int c = 0; c < kSvcClasses; ++c) j->class_groups[c] = totals[2 + c];
+    for (int c = 0; c < kSvcSegs; ++c) j->class_groups[c] = totals[2 + c];
     *nvec = totals[0];
     *job = j;
     return 0;
@@ -591,7 +591,7 @@ int svc_replayed_rows(svc_job* j, int64_t* rows) {
     g_err[0] = 0;
     if (!j || !rows) return (int)cudaErrorInvalidValue;
     *rows = 0;
-    for (int c = 1; c < kSvcClasses; ++c) *rows += j->class_groups[c];       // every class but "ascending"
+    for (int c = 1; c < kSvcSegs; ++c) *rows += j->class_groups[c];       // every class but "ascending"
     return 0;
 }
 

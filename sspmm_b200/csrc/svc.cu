@@ -66,6 +66,7 @@ constexpr int kSCapU = 306, kSCapT = 512;
 constexpr int kM1CapU = 1228, kM1CapT = 2048;
 constexpr int kM2CapU = 4914, kM2CapT = 8192;
 constexpr int kLCapT = 32768;
+constexpr int kLStateless = 19660;   // most keys a table of kLCapT slots holds
 constexpr int kLSeqInts = 19664;    // a table of kLCapT slots holds fewer than 19661 keys; class L keeps the level's sequence in shared memory
 constexpr int kListsPerGroup = 4;   // X2, NEW, P, Q (the fifth list is the output slice)
 
@@ -91,13 +92,52 @@ __host__ __device__ inline int final_table_len(int distinct) {
 }
 
 __host__ __device__ inline int replay_class(int u, int tbl_len) {
-    if (tbl_len == 0) return kClassSorted;
+    if (tbl_len <= 0) return kClassSorted;
     if (u <= kXSCapU) return kClassXS;
     if (u <= kSCapU) return kClassS;
     if (u <= kM1CapU) return kClassM1;
     if (u <= kM2CapU) return kClassM2;
     if (tbl_len <= kLCapT) return kClassL;
     return kClassXL;
+}
+
+// The list of replayed groups is written segment by segment.  A segment is a class, or a part of one: the groups
+// of a class differ in cost by the ratio of their sizes (up to four), and with only a few groups per team the order
+// in which the work counter hands them out decides how long the last team runs.  So the classes with few, long
+// groups are cut into four size ranges (two for S) that are listed largest first.
+constexpr int kNumSegs = kSvcSegs;
+constexpr int kSegS = 1, kSegM1 = 3, kSegM2 = 7, kSegL = 11, kSegXL = 15, kSegXS = 16, kSegSortedBig = 17;
+static_assert(kNumSegs == 18, "segment numbering");
+// Groups in ascending order with more than kBigGroup entries get a CTA each; the counting pass marks them
+// (table length -1) and the last segment lists them.
+__host__ __device__ inline int size_quarter(int u, int cap) {       // 0 = the largest sizes of a class whose largest is cap
+    if (u > (int)((long long)cap * 181 / 256)) return 0;            // cap / sqrt(2)
+    if (u > cap / 2) return 1;
+    if (u > (int)((long long)cap * 91 / 256)) return 2;             // cap / (2 sqrt(2))
+    return 3;
+}
+__host__ __device__ inline int list_segment(int u, int tbl_len) {
+    switch (replay_class(u, tbl_len)) {
+        case kClassS: return kSegS + (u > kSCapU / 2 ? 0 : 1);
+        case kClassM1: return kSegM1 + size_quarter(u, kM1CapU);
+        case kClassM2: return kSegM2 + size_quarter(u, kM2CapU);
+        case kClassL: return kSegL + size_quarter(u, kLStateless);
+        case kClassXL: return kSegXL;
+        case kClassXS: return kSegXS;
+        default: return tbl_len < 0 ? kSegSortedBig : 0;
+    }
+}
+// first segment of a class and one past its last
+__host__ inline void class_segments(int c, int& s0, int& s1) {
+    switch (c) {
+        case kClassS: s0 = kSegS; s1 = kSegM1; break;
+        case kClassM1: s0 = kSegM1; s1 = kSegM2; break;
+        case kClassM2: s0 = kSegM2; s1 = kSegL; break;
+        case kClassL: s0 = kSegL; s1 = kSegXL; break;
+        case kClassXL: s0 = kSegXL; s1 = kSegXS; break;
+        case kClassXS: s0 = kSegXS; s1 = kSegSortedBig; break;
+        default: s0 = 0; s1 = 1; break;
+    }
 }
 
 // Global scratch ints of one replayed group.
@@ -261,7 +301,7 @@ svc_count_kernel(SvcProblem p, int words, int filter, int* __restrict__ counts, 
             const int len = final_table_len(cnt);
             const int replay = (mx >= len) ? 1 : 0;
             mode[i] = replay;
-            tbl_len[i] = replay ? len : 0;
+            tbl_len[i] = replay ? len : ((e1 - e0) > kBigGroup ? -1 : 0);     // -1: ascending order, and large enough for a CTA
             if (bad) g_svc_bad_column = 1;
         }
         Team::sync();
@@ -273,11 +313,12 @@ svc_count_kernel(SvcProblem p, int words, int filter, int* __restrict__ counts, 
 // groups per class, in three small launches: per-block sums, a scan of the block sums by one CTA, and the final
 // positions.  A block covers kScanBlock groups; a block sum is kScanFields numbers: vectors, scratch ints, and
 // the groups of each replay class.
-// totals: [0] nvec, [1] scratch ints, [2..2+kNumClasses) groups per replay class, then the bad-column flag
+// totals: [0] nvec, [1] scratch ints, [2..2+kNumSegs) groups per list segment, then the bad-column flag
 constexpr int kScanThreads = 1024;
 constexpr int kScanPerThread = 4;
 constexpr int kScanBlock = kScanThreads * kScanPerThread;
-constexpr int kScanFields = 2 + kNumClasses;
+constexpr int kScanFields = 2 + kNumSegs;
+static_assert(kScanFields == kSvcScanFields, "scan fields");
 
 // Sums `v` over the block; the result is valid in every thread.  sh: 32 long longs.
 __device__ __forceinline__ long long block_sum_ll(long long v, long long* sh) {
@@ -323,9 +364,9 @@ svc_scan_sums_kernel(int m_vec, const int* __restrict__ counts, const int* __res
         const int u = counts[i], len = tbl_len[i];
         f[0] += u;
         f[1] += group_scratch_ints(u, len);
-        const int c = replay_class(u, len);
+        const int c = list_segment(u, len);
 #pragma unroll
-        for (int k = 0; k < kNumClasses; ++k) f[2 + k] += (c == k) ? 1 : 0;
+        for (int k = 0; k < kNumSegs; ++k) f[2 + k] += (c == k) ? 1 : 0;
     }
 #pragma unroll
     for (int k = 0; k < kScanFields; ++k) {
@@ -361,7 +402,7 @@ svc_scan_blocks_kernel(int n_blocks, long long* __restrict__ block_sums, long lo
 }
 
 // vec_ptr: counts in, exclusive scan out (and the total at [m_vec]); tbl_off: scratch offsets; class_list: the
-// replayed groups class by class (S first), inside a class in ascending order.
+// replayed groups segment by segment (see list_segment), inside a segment in ascending order.
 __global__ void __launch_bounds__(kScanThreads)
 svc_scan_place_kernel(int m_vec, int* __restrict__ vec_ptr, const int* __restrict__ tbl_len,
                       long long* __restrict__ tbl_off, const long long* __restrict__ block_sums,
@@ -381,21 +422,21 @@ svc_scan_place_kernel(int m_vec, int* __restrict__ vec_ptr, const int* __restric
             u[j] = vec_ptr[i];
             const int len = tbl_len[i];
             scr[j] = group_scratch_ints(u[j], len);
-            cls[j] = replay_class(u[j], len);
+            cls[j] = list_segment(u[j], len);
             f[0] += u[j];
             f[1] += scr[j];
 #pragma unroll
-            for (int k = 0; k < kNumClasses; ++k) f[2 + k] += (cls[j] == k) ? 1 : 0;
+            for (int k = 0; k < kNumSegs; ++k) f[2 + k] += (cls[j] == k) ? 1 : 0;
         }
     }
-    // where class c starts in the list: after all groups of the classes before it (class 0 is not replayed)
+    // where segment k starts in the list: after all groups of the segments before it (segment 0 is not replayed)
     long long at[kScanFields];
 #pragma unroll
     for (int k = 0; k < kScanFields; ++k)
         at[k] = block_sums[(size_t)blockIdx.x * kScanFields + k] + block_prefix_ll(f[k], sh);
     long long class_base = 0;
 #pragma unroll
-    for (int k = 1; k < kNumClasses; ++k) {
+    for (int k = 1; k < kNumSegs; ++k) {
         at[2 + k] += class_base;
         class_base += totals[2 + k];
     }
@@ -408,7 +449,7 @@ svc_scan_place_kernel(int m_vec, int* __restrict__ vec_ptr, const int* __restric
         at[0] += u[j];
         at[1] += scr[j];
 #pragma unroll
-        for (int k = 1; k < kNumClasses; ++k)
+        for (int k = 1; k < kNumSegs; ++k)
             if (cls[j] == k) class_list[at[2 + k]++] = i;
     }
     if (blockIdx.x == 0 && threadIdx.x == 0) {
@@ -421,13 +462,17 @@ svc_scan_place_kernel(int m_vec, int* __restrict__ vec_ptr, const int* __restric
 template <class Team>
 __global__ void __launch_bounds__(256)
 svc_emit_sorted_kernel(SvcProblem p, int words, int filter, const int* __restrict__ vec_ptr,
-                       const int* __restrict__ mode, int* __restrict__ out_col, __half* __restrict__ out_vals) {
+                       const int* __restrict__ mode, int* __restrict__ out_col, __half* __restrict__ out_vals,
+                       const int* __restrict__ list, int n_list) {
     extern __shared__ unsigned int sm_words[];
     __shared__ int red[33];
     unsigned int* bm = sm_words + (size_t)Team::index_in_block() * words * 2;
     unsigned int* pre = bm + words;
     const int tid = Team::tid();
-    for (int i = blockIdx.x * Team::kPerBlock + Team::index_in_block(); i < p.m_vec; i += gridDim.x * Team::kPerBlock) {
+    // with a list: only the groups it names; else every group
+    const int n_loop = list ? n_list : p.m_vec;
+    for (int k = blockIdx.x * Team::kPerBlock + Team::index_in_block(); k < n_loop; k += gridDim.x * Team::kPerBlock) {
+        const int i = list ? list[k] : k;
         if (mode[i] != 0) continue;
         const int r0 = min(i * p.V, p.M), r1 = min(i * p.V + p.V, p.M);
         const int e0 = p.row_ptr[r0], e1 = p.row_ptr[r1];
@@ -992,7 +1037,7 @@ cudaError_t svc_count_and_scan(const SvcProblem& p, const SvcScratch& s, bool /*
     return cudaGetLastError();
 }
 
-cudaError_t svc_emit(const SvcProblem& p, const SvcScratch& s, const long long* class_groups, int* out_col,
+cudaError_t svc_emit(const SvcProblem& p, const SvcScratch& s, const long long* seg_groups, int* out_col,
                      __half* out_vals, cudaStream_t stream) {
     if (p.m_vec == 0) return cudaSuccess;
     const int sms = device_sm_count();
@@ -1007,23 +1052,39 @@ cudaError_t svc_emit(const SvcProblem& p, const SvcScratch& s, const long long* 
     if (e != cudaSuccess) return e;
     std::lock_guard<std::mutex> lk(g_aux_mu);
     Fork f(aux_for_device(), stream);
+    // groups per class and where the class starts in the list of replayed groups
+    long long class_groups[kNumClasses] = {0}, first[kNumClasses] = {0};
+    class_groups[kClassSorted] = seg_groups[0] + seg_groups[kSegSortedBig];
+    long long big_first = 0;                       // the ascending groups that may need a CTA: last segment of the list
+    for (int k = 1; k < kSegSortedBig; ++k) big_first += seg_groups[k];
+    const int* big_list = s.class_list + big_first;
+    const int n_big = (int)seg_groups[kSegSortedBig];
+    for (int c = 1; c < kNumClasses; ++c) {
+        int s0, s1;
+        class_segments(c, s0, s1);
+        for (int k = 1; k < s0; ++k) first[c] += seg_groups[k];
+        for (int k = s0; k < s1; ++k) class_groups[c] += seg_groups[k];
+    }
     if (class_groups[kClassSorted] > 0) {
         const size_t warp_smem = (size_t)WarpTeam::kPerBlock * words * 8;
         if (p.m_vec <= 16 * sms || warp_smem > 200 * 1024) {
             const int grid = p.m_vec < sms * 16 ? p.m_vec : sms * 16;
-            svc_emit_sorted_kernel<BlockTeam<256>><<<grid, 256, (size_t)words * 8, stream>>>(p, words, 0, s.vec_ptr, s.mode, out_col, out_vals);
+            svc_emit_sorted_kernel<BlockTeam<256>><<<grid, 256, (size_t)words * 8, stream>>>(p, words, 0, s.vec_ptr, s.mode, out_col, out_vals,
+                                                                                             nullptr, 0);
         } else {
             int grid = (p.m_vec + WarpTeam::kPerBlock - 1) / WarpTeam::kPerBlock;
             if (grid > sms * 8) grid = sms * 8;
-            svc_emit_sorted_kernel<WarpTeam><<<grid, 256, warp_smem, stream>>>(p, words, 1, s.vec_ptr, s.mode, out_col, out_vals);
-            svc_emit_sorted_kernel<BlockTeam<256>><<<sms * 2, 256, (size_t)words * 8, f.next()>>>(p, words, 2, s.vec_ptr, s.mode, out_col, out_vals);
+            svc_emit_sorted_kernel<WarpTeam><<<grid, 256, warp_smem, stream>>>(p, words, 1, s.vec_ptr, s.mode, out_col, out_vals, nullptr, 0);
+            if (n_big > 0) {
+                const int big_grid = n_big < sms * 2 ? n_big : sms * 2;
+                svc_emit_sorted_kernel<BlockTeam<256>><<<big_grid, 256, (size_t)words * 8, f.next()>>>(p, words, 2, s.vec_ptr, s.mode, out_col,
+                                                                                                     out_vals, big_list, n_big);
+            }
         }
         e = cudaGetLastError();
         if (e != cudaSuccess) return e;
     }
     // where each class starts in the list of replayed groups (the order svc_scan_place_kernel writes them in)
-    long long first[kNumClasses] = {0};
-    for (int c = 2; c < kNumClasses; ++c) first[c] = first[c - 1] + class_groups[c - 1];
     // the largest groups first: they are the critical path
     e = launch_replay<BlockTeam<1024>, kClassXL>(p, s, out_col, out_vals, class_groups[kClassXL], first[kClassXL], 0, 0, f.next());
     if (e == cudaSuccess)

@@ -26,9 +26,9 @@ struct SvcProblem {
 struct SvcScratch {
     int* vec_ptr;         // [m_vec+1]  counts, then exclusive scan = vector row pointers
     int* mode;            // [m_vec]    0 = ascending order is exact, 1 = replay the hash table
-    int* tbl_len;         // [m_vec]    final table length of replayed groups (0 otherwise)
+    int* tbl_len;         // [m_vec]    final table length of replayed groups (0 otherwise; -1: ascending and large)
     long long* tbl_off;   // [m_vec+1]  exclusive scan of per-group table scratch
-    long long* totals;    // [kSvcTotals] {nvec, scratch ints, groups per replay class (kSvcClasses), bad-column flag}
+    long long* totals;    // [kSvcTotals] {nvec, scratch ints, groups per list segment (kSvcSegs; [0] = ascending order), bad-column flag}
     int* tables;          // [totals[1]] replay scratch, allocated after the counting pass
     int* class_list;      // [m_vec]    replayed groups, class by class (written by the scan)
     int* queue;           // [8]        work counters of the replay classes
@@ -39,14 +39,15 @@ struct SvcScratch {
 inline long long svc_scan_blocks(long long m_vec) { return m_vec > 0 ? (m_vec + 4095) / 4096 : 1; }
 
 constexpr int kSvcClasses = 7;                 // ascending order, and six size classes of replayed groups
-constexpr int kSvcTotals = 3 + kSvcClasses;
-constexpr int kSvcScanFields = 2 + kSvcClasses;  // numbers per block of the scans
+constexpr int kSvcSegs = 18;                   // segments of the list of replayed groups (classes, some cut by size)
+constexpr int kSvcTotals = 3 + kSvcSegs;
+constexpr int kSvcScanFields = 2 + kSvcSegs;   // numbers per block of the scans
 
 // Pass 1: per-group distinct counts, mode decision, scans.  Asynchronous on `stream`.
 cudaError_t svc_count_and_scan(const SvcProblem& p, const SvcScratch& s, bool with_values, cudaStream_t stream);
 // Pass 2: emits column lists (and value vectors when out_vals != null; out_vals must be zero-filled).
-// class_groups = totals[2..2+kSvcClasses) read back by the host (launches are skipped for empty classes).
-cudaError_t svc_emit(const SvcProblem& p, const SvcScratch& s, const long long* class_groups, int* out_col,
+// seg_groups = totals[2..2+kSvcSegs) read back by the host (launches are skipped for empty classes).
+cudaError_t svc_emit(const SvcProblem& p, const SvcScratch& s, const long long* seg_groups, int* out_col,
                      __half* out_vals, cudaStream_t stream);
 
 // ---- batches: several independent matrices compressed as one stacked matrix ----------------
