@@ -1220,6 +1220,19 @@ int sspmm_group_create(const sspmm_group_item* items, int count, int out_is_f16,
         const fused::Problem& L = probs[lead];
         int parts = (tiles < 8 * (int64_t)units && L.k_steps > cut) ? (L.k_steps + cut - 1) / cut : 1;
         if (parts > 16) parts = 16;
+        if (count == 1) {
+            // One product: the number of parts that gives the shortest critical path.  An item costs its K steps
+            // plus two for the hand-over, and a cut tile pays for its fp32 partial tiles (written once, read once:
+            // measured about 17 K steps' worth per part for a 128 x 256 tile when every SM does it at once).
+            const int64_t t = (int64_t)L.m_tiles * L.n_tiles;
+            const int64_t extra = 17 * BN / 256 + 1;
+            int64_t best = -1;
+            for (int q = 1; q <= 16 && q <= L.k_steps; ++q) {
+                const int64_t rounds = (t * q + units - 1) / units;
+                const int64_t cost = rounds * ((L.k_steps + q - 1) / q + 2 + (q > 1 ? extra : 0));
+                if (best < 0 || cost < best) { best = cost; parts = q; }
+            }
+        }
         const int sps = (L.k_steps + parts - 1) / parts;
         parts = (L.k_steps + sps - 1) / sps;
         for (int nt = 0; nt < L.n_tiles; ++nt)
