@@ -51,6 +51,10 @@ constexpr int kGroupThreads = 128;
 constexpr int kEpilogueWarp0 = 4;
 constexpr int kLoaderWarp0 = 8;
 constexpr int kPublishAhead = 16;       // items the scheduler keeps published ahead of the B producer (< kRing)
+// With A fetched by TMA nobody looks further ahead than the next item, and every item published early is an item
+// claimed early: sixteen claimed items per CTA is the whole work list of a small group, dealt out before anybody
+// knows who will be free.  (Measured on the conv step at the 8-GPU shard width: CTAs ended between 112 and 156 us.)
+constexpr int kPublishAheadTma = 2;
 constexpr int kThreads = kLoaderWarp0 * 32 + kLoaderGroups * kGroupThreads;
 // Work items are published ahead of their use.  A loader thread looks four of its own stages ahead, which with
 // one-step items is a dozen items past the stage it is about to store, while the epilogue may still hold the
@@ -369,7 +373,7 @@ sspmm_fused_kernel(const __grid_constant__ Params gp) {
             Item it;
             for (uint32_t n = 0; ok; ++n) {
                 if (!publish(n + 1, true)) break;                // the item this thread is about to load
-                publish(n + 1 + kPublishAhead, false);           // and, ring permitting, the ones the loaders look ahead to
+                publish(n + 1 + (ATMA ? kPublishAheadTma : kPublishAhead), false);   // and, ring permitting, the ones the loaders look ahead to
                 if (!take_item(n, it, false)) break;
                 const Problem* P = problem_of(it.prob);
                 if (gp.probs && it.prob != last_prob) {
@@ -420,7 +424,7 @@ sspmm_fused_kernel(const __grid_constant__ Params gp) {
                         for (int c = 0; c < chunks; ++c) tma_load_3d(b_s + c * L::kChunk, &P->tmap_b, n0 + 64 * c, ks * kBK, 0, full);
                     }
                     if (++stage == BSTAGES) { stage = 0; phase ^= 1u; }
-                    if ((ks & 7) == 7) publish(n + 1 + kPublishAhead, false);
+                    if ((ks & 7) == 7) publish(n + 1 + (ATMA ? kPublishAheadTma : kPublishAhead), false);
                 }
             }
         }

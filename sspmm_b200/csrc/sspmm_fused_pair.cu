@@ -151,7 +151,7 @@ sspmm_fused_pair_kernel(const __grid_constant__ Params gp) {
             for (uint32_t n = 0; ok; ++n) {
                 if (rank == 0) {
                     if (!publish(n + 1, true)) break;
-                    publish(n + 1 + kPublishAhead, false);
+                    publish(n + 1 + kPublishAheadTma, false);
                 }
                 if (!take_item(n, it, false)) break;
                 const Problem* P = problem_of(it.prob);
@@ -201,7 +201,7 @@ sspmm_fused_pair_kernel(const __grid_constant__ Params gp) {
                             tma_load_3d_pair(b_s + c * L::kChunk, &P->tmap_b1, n0 + (int)rank * half + 64 * c, ks * kBK, 0, full);
                     }
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
-                    if (rank == 0 && (ks & 7) == 7) publish(n + 1 + kPublishAhead, false);
+                    if (rank == 0 && (ks & 7) == 7) publish(n + 1 + kPublishAheadTma, false);
                 }
             }
         }
