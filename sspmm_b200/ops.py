@@ -218,8 +218,10 @@ def sspmm_planned(plan: Plan, values: torch.Tensor, rhs: torch.Tensor, out_dtype
 class Group:
     """Several products bound to their operands and run as ONE persistent launch (``sspmm_group_create`` /
     ``sspmm_group_run``).  ``products`` is a list of (plan, values, rhs, out); all outputs share one dtype.
-    ``mode``: COMPRESSED builds the A tiles inside the kernel (one launch, no scratch for A), EXPANDED writes dense
-    copies of A first (two launches, faster per K step), AUTO picks by the work per SM."""
+    ``mode``: COMPRESSED builds the A tiles inside the kernel from the compressed operand (no scratch for A),
+    EXPANDED lets the kernel's loader warps write dense copies of A while the first tiles are multiplied (faster per
+    K step), PAIRS is EXPANDED with 256 x 256 tiles on CTA pairs, AUTO picks COMPRESSED or EXPANDED by the work per
+    SM.  Every mode is one launch per run."""
 
     AUTO, COMPRESSED, EXPANDED, PAIRS = 0, 1, 2, 3
 
