@@ -127,6 +127,19 @@ def test_sorted_row_swizzle(lib):
     assert np.array_equal(got, svc_oracle.sorted_row_swizzle(r.vec_row_ptr))
 
 
+@pytest.mark.parametrize("m_vec", [8192, 8193, 100_000, 262_144])
+def test_sorted_row_swizzle_many_rows(lib, m_vec):
+    """Around and far above the row count where the rank loop gives way to the sort: order = length descending, row id
+    ascending among equal lengths (many ties: lengths are drawn from 0..40), a permutation of all rows."""
+    rng = np.random.default_rng(m_vec)
+    lens = rng.integers(0, 41, m_vec)
+    lens[rng.integers(0, m_vec, 5)] = rng.integers(1000, 100000, 5)
+    ptr = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    got = ops.sorted_row_swizzle(torch.from_numpy(ptr).to("cuda:0")).cpu().numpy()
+    want = np.lexsort((np.arange(m_vec), -lens))
+    assert np.array_equal(got, want)
+
+
 def test_svc_full_size_properties(lib):
     """n = 65536 power-law matrix (largest sweep size): checked through
     size-independent properties instead of the slow CPU oracle."""
