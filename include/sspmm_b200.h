@@ -269,6 +269,8 @@ int svc_replayed_rows(svc_job* job, int64_t* rows);
  * Row swizzle: vector rows by decreasing length, ties by increasing row id.
  * Replaces SortedRowSwizzle, SSpMM/include/bm_test_utils.h:210-225 (std::sort
  * there leaves the order of ties unspecified).  d_row_indices[m_vec].
+ * Asynchronous on stream.  Above 8192 vector rows the rows are sorted, with
+ * 8 bytes of scratch per row (next power of two) from the stream-ordered pool.
  */
 int sspmm_sorted_row_swizzle(int m_vec, const int* d_row_offsets, int* d_row_indices, void* stream);
 
