@@ -66,7 +66,7 @@ constexpr int kSCapU = 306, kSCapT = 512;
 constexpr int kM1CapU = 1228, kM1CapT = 2048;
 constexpr int kM2CapU = 4914, kM2CapT = 8192;
 constexpr int kLCapT = 32768;
-constexpr int kLStateless = 19660;   // most keys a table of kLCapT slots holds
+constexpr int kLCapU = 19660;   // most keys a table of kLCapT slots holds
 constexpr int kLSeqInts = 19664;    // a table of kLCapT slots holds fewer than 19661 keys; class L keeps the level's sequence in shared memory
 constexpr int kListsPerGroup = 4;   // X2, NEW, P, Q (the fifth list is the output slice)
 
@@ -121,7 +121,7 @@ __host__ __device__ inline int list_segment(int u, int tbl_len) {
         case kClassS: return kSegS + (u > kSCapU / 2 ? 0 : 1);
         case kClassM1: return kSegM1 + size_quarter(u, kM1CapU);
         case kClassM2: return kSegM2 + size_quarter(u, kM2CapU);
-        case kClassL: return kSegL + size_quarter(u, kLStateless);
+        case kClassL: return kSegL + size_quarter(u, kLCapU);
         case kClassXL: return kSegXL;
         case kClassXS: return kSegXS;
         default: return tbl_len < 0 ? kSegSortedBig : 0;
@@ -662,10 +662,6 @@ __device__ int extract_ordered(int* tab, int size, const int* seq, int* dst, int
     Team::sync();
     return n;
 }
-
-// Fill at which the 128-slot table grows to 512: up to here one thread inserts sequentially
-// (three tiny tables are not worth a team-wide pass each).
-constexpr int kSeqPrefix = 77;
 
 // Sequential replay by one thread (used when a matrix row lists a column twice; rare).  tab holds keys.
 __device__ int replay_sequential(const SvcProblem& p, int r0, int r1, int* tab, int cap, int* xa, int* xb, int* tmp) {
