@@ -373,7 +373,10 @@ sspmm_fused_kernel(const __grid_constant__ Params gp) {
             Item it;
             for (uint32_t n = 0; ok; ++n) {
                 if (!publish(n + 1, true)) break;                // the item this thread is about to load
-                publish(n + 1 + (ATMA ? kPublishAheadTma : kPublishAhead), false);   // and, ring permitting, the ones the loaders look ahead to
+                // and, ring permitting, the ones further ahead: at once when the loader warps look ahead to them;
+                // with A by TMA only after this item's first loads are on their way (fetching a work item is a
+                // round trip to L2 that nothing else of this thread waits for)
+                publish(n + 1 + (ATMA ? kPublishAheadTma : kPublishAhead), false);
                 if (!take_item(n, it, false)) break;
                 const Problem* P = problem_of(it.prob);
                 if (gp.probs && it.prob != last_prob) {
@@ -424,7 +427,8 @@ sspmm_fused_kernel(const __grid_constant__ Params gp) {
                         for (int c = 0; c < chunks; ++c) tma_load_3d(b_s + c * L::kChunk, &P->tmap_b, n0 + 64 * c, ks * kBK, 0, full);
                     }
                     if (++stage == BSTAGES) { stage = 0; phase ^= 1u; }
-                    if ((ks & 7) == 7) publish(n + 1 + (ATMA ? kPublishAheadTma : kPublishAhead), false);
+                    if ((ks & 7) == 7)
+                        publish(n + 1 + (ATMA ? kPublishAheadTma : kPublishAhead), false);
                 }
             }
         }
@@ -477,18 +481,20 @@ sspmm_fused_kernel(const __grid_constant__ Params gp) {
         if (gp.jobs) {
             const int t = threadIdx.x - kLoaderWarp0 * 32;
             constexpr int kExpandThreads = kLoaderGroups * kGroupThreads;
+            // The request for the next block number is made while the current block is written (its answer is
+            // only needed in the next round), and the job of a block is found by walking on from the last one: a
+            // round is then one chain of metadata -> value vectors -> stores, not three.
+            int claimed = 0, job_at = 0;
+            if (t == 0) claimed = atomicAdd(gp.expand_state, 1);
             for (;;) {
-                if (t == 0) *bcast2 = atomicAdd(gp.expand_state, 1);
+                if (t == 0) *bcast2 = claimed;
                 named_barrier_sync(3, kExpandThreads);
                 const int vb = *bcast2;
                 named_barrier_sync(3, kExpandThreads);            // everyone has read the number before the next one is written
                 if (vb >= gp.expand_blocks) break;
-                int lo = 0, hi = gp.n_jobs - 1;
-                while (lo < hi) {
-                    const int mid = (lo + hi + 1) >> 1;
-                    if (__ldg(&gp.jobs[mid].block_base) <= vb) lo = mid; else hi = mid - 1;
-                }
-                const ExpandJob job = gp.jobs[lo];
+                if (t == 0) claimed = atomicAdd(gp.expand_state, 1);
+                while (job_at + 1 < gp.n_jobs && __ldg(&gp.jobs[job_at + 1].block_base) <= vb) ++job_at;
+                const ExpandJob job = gp.jobs[job_at];
                 const int id = (vb - job.block_base) * kExpandThreads + t;
                 if (job.V == 16) expand_slots<16>(job, id); else expand_slots<8>(job, id);
                 __threadfence();
@@ -1206,7 +1212,12 @@ int sspmm_group_create(const sspmm_group_item* items, int count, int out_is_f16,
     // fetch the panel from HBM once and from L2 afterwards.
     std::vector<int> order((size_t)count);
     for (int i = 0; i < count; ++i) order[i] = i;
-    std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return probs[a].k_steps > probs[b].k_steps; });
+    // Among products of equal depth those with the longer vectors go first: their dense copies take half as many
+    // expansion blocks per tile, so the CTAs that start on them wait less for the first copies.
+    std::stable_sort(order.begin(), order.end(), [&](int a, int b) {
+        if (probs[a].k_steps != probs[b].k_steps) return probs[a].k_steps > probs[b].k_steps;
+        return items[a].plan->V > items[b].plan->V;
+    });
     std::vector<char> placed((size_t)count, 0);
     for (int oi = 0; oi < count; ++oi) {
         if (placed[(size_t)order[oi]]) continue;
