@@ -302,6 +302,9 @@ sspmm_fused_kernel(const __grid_constant__ Params gp) {
         tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_ptr_smem)), L::kTmemCols);
         tmem_relinquish();
     }
+    // The number of the first expansion block is asked for now: the answer is on its way while the barriers are set up.
+    int first_expand_block = 0;
+    if (ATMA && gp.jobs && threadIdx.x == kLoaderWarp0 * 32) first_expand_block = atomicAdd(gp.expand_state, 1);
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
@@ -484,8 +487,7 @@ sspmm_fused_kernel(const __grid_constant__ Params gp) {
             // The request for the next block number is made while the current block is written (its answer is
             // only needed in the next round), and the job of a block is found by walking on from the last one: a
             // round is then one chain of metadata -> value vectors -> stores, not three.
-            int claimed = 0, job_at = 0;
-            if (t == 0) claimed = atomicAdd(gp.expand_state, 1);
+            int claimed = first_expand_block, job_at = 0;
             for (;;) {
                 if (t == 0) *bcast2 = claimed;
                 named_barrier_sync(3, kExpandThreads);
